@@ -1,0 +1,167 @@
+/*
+ * mhc_b200.h — C ABI of the B200-native mHC layer kernels (libmhc_b200.so).
+ *
+ * Every entry point takes raw DEVICE pointers, plain sizes, a dtype tag, a caller-provided
+ * workspace and a cudaStream_t.  Nothing here allocates, synchronises the host, owns global
+ * state or terminates the process: each call validates its arguments, enqueues its kernels on
+ * `stream` and returns an `mhc_status` (0 = ok).  All tensors are dense, row-major, and must be
+ * 16-byte aligned.  The calls are re-entrant and may be used from several host threads / devices
+ * as long as each call is given its own workspace.
+ *
+ * Citations "replaces <file:line>" name the function of AndreSlavescu/mHC.cu whose job the entry
+ * point takes over (paths relative to that project).
+ *
+ * Vocabulary: B = tokens, n = residual streams (expansion rate, 1..32), C = hidden size,
+ * K = 2n + n*n projection outputs per token in the order (pre[n], post[n], res[n*n]).
+ */
+#ifndef MHC_B200_H_
+#define MHC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cudaStream_t without pulling in cuda_runtime.h */
+typedef struct CUstream_st* mhc_stream_t;
+
+/* element type of the [B,n,C] streams (x, y, dy, dx) and of phi */
+enum mhc_dtype { MHC_F32 = 0, MHC_BF16 = 1 };
+
+enum mhc_status {
+    MHC_OK = 0,
+    MHC_ERR_NULL_POINTER = 1,  /* a required pointer is NULL */
+    MHC_ERR_BAD_SHAPE = 2,     /* B < 0, n outside 1..32, C < 1, iters < 0, or sizes overflow */
+    MHC_ERR_BAD_DTYPE = 3,     /* dtype tag is not MHC_F32 / MHC_BF16 */
+    MHC_ERR_MISALIGNED = 4,    /* a tensor pointer or the workspace is not 16-byte aligned */
+    MHC_ERR_WORKSPACE = 5,     /* workspace_bytes is smaller than mhc_workspace_bytes(...) */
+    MHC_ERR_UNSUPPORTED = 6,   /* valid request this build has no kernel for */
+    MHC_ERR_CUDA = 7,          /* a CUDA runtime call / launch reported an error */
+    MHC_ERR_LIMIT = 8          /* size beyond a fixed capacity stated by the entry point */
+};
+
+/* which call a workspace is sized for */
+enum mhc_op {
+    MHC_OP_DYNAMIC_FWD = 0,
+    MHC_OP_DYNAMIC_BWD = 1,
+    MHC_OP_STATIC_FWD = 2,
+    MHC_OP_STATIC_BWD = 3,
+    MHC_OP_SINKHORN_FWD = 4,
+    MHC_OP_SINKHORN_BWD = 5,
+    MHC_OP_RMSNORM_FWD = 6,
+    MHC_OP_RMSNORM_BWD = 7
+};
+
+/* Human-readable text for an mhc_status.  Never NULL.
+ * Replaces the CHECK_CUDA / CHECK_CUBLAS macros that print and exit()
+ * (src/csrc/include/mhc_types.h:25-40). */
+const char* mhc_status_string(int status);
+
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* mhc_last_cuda_error(void);
+
+/* ABI revision; bumped when a signature changes. */
+int mhc_abi_version(void);
+
+/* Bytes of scratch a call needs for the given problem (0 is a valid answer).  For the
+ * Sinkhorn ops pass B = batch, n = matrix size, C = 0.  Returns (size_t)-1 on bad arguments.
+ * Replaces the grow-on-demand global MHCWorkspace (src/python/bindings.cu:166-219). */
+size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int dtype);
+
+/* ---------------------------------------------------------------------------------------------
+ * Dynamic-H layer, forward.  Replaces mhc_layer_fwd_dynamic (src/python/bindings.cu:403-481) and
+ * the host-side packing in MHCLayerDynamicFunction.forward (src/python/mhc/ops.py:156-237).
+ *
+ *   r      = sqrt(mean(x_flat^2) + eps)                 x_flat = x viewed as [B, n*C]
+ *   p      = (x_flat / r) @ phi^T                        [B, K]
+ *   t      = alpha_k * p + bias
+ *   H_pre  = sigmoid(t_pre)   H_post = 2*sigmoid(t_post)   M = Sinkhorn(exp(t_res), iters, eps)
+ *   a      = sum_i H_pre[i] x[i,:]     rho = sqrt(mean(a^2) + eps)
+ *   y[i,:] = sum_j M[i,j] x[j,:] + H_post[i] * (a / rho * w)
+ *
+ * out:  y [B,n,C] dtype;  saved for backward (all fp32): rms [B] (= rho), rms_h [B] (= r),
+ *       H_pre [B,n], H_post [B,n], M [B,n,n], proj [B,K] (= p).
+ * in:   x [B,n,C] dtype;  rmsnorm_weight [C] bf16;  phi [K, n*C] dtype (rows: pre, post, res);
+ *       alpha [3] fp32 on the device (pre, post, res);  bias [K] fp32 (b_pre, b_post, b_res).
+ * alpha lives on the device so that no host synchronisation is needed
+ * (the reference reads it with .item(), src/python/mhc/ops.py:178-188). */
+int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+                    float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                    const float* alpha, const float* bias, int64_t B, int n, int64_t C, int iters,
+                    float eps, int dtype, void* workspace, size_t workspace_bytes,
+                    mhc_stream_t stream);
+
+/* Dynamic-H layer, backward: exact gradients of everything above.  Replaces
+ * mhc_layer_bwd_dynamic (src/python/bindings.cu:483-542) together with the eager PyTorch tail of
+ * MHCLayerDynamicFunction.backward (src/python/mhc/ops.py:276-361, incl. its per-token Python loop).
+ *
+ * out:  dx [B,n,C] dtype;  fp32 parameter gradients, each written (not accumulated):
+ *       d_rmsnorm_weight [C], d_phi [K, n*C], d_alpha [3], d_bias [K].  They may be slices of one
+ *       flat bucket that is then all-reduced across data-parallel ranks.
+ * in:   dy, x [B,n,C] dtype;  the forward's parameters and saved tensors. */
+int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha, float* d_bias,
+                    const void* dy, const void* x, const void* rmsnorm_weight, const void* phi,
+                    const float* alpha, const float* bias, const float* rms, const float* rms_h,
+                    const float* H_pre, const float* H_post, const float* M, const float* proj,
+                    int64_t B, int n, int64_t C, int iters, float eps, int dtype, void* workspace,
+                    size_t workspace_bytes, mhc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Static-H layer, forward: one set of coefficients shared by all tokens,
+ * H_pre_act = sigmoid(H_pre), H_post_act = 2*sigmoid(H_post), M = Sinkhorn(exp(H_res)).
+ * Replaces mhc_layer_fwd (src/python/bindings.cu:264-328); with rms == NULL it is the
+ * inference call mhc_layer_fwd_inference (src/python/bindings.cu:221-262), in which case
+ * H_pre_act / H_post_act / M may also be NULL (they then live in the workspace).
+ *
+ * out:  y [B,n,C] dtype;  rms [B];  H_pre_act [n], H_post_act [n], M [n,n]  (fp32)
+ * in:   x [B,n,C] dtype;  rmsnorm_weight [C] bf16;  H_pre [n], H_post [n], H_res [n,n] fp32 raw. */
+int mhc_static_fwd(void* y, float* rms, float* H_pre_act, float* H_post_act, float* M,
+                   const void* x, const void* rmsnorm_weight, const float* H_pre,
+                   const float* H_post, const float* H_res, int64_t B, int n, int64_t C, int iters,
+                   float eps, int dtype, void* workspace, size_t workspace_bytes,
+                   mhc_stream_t stream);
+
+/* Static-H layer, backward.  Replaces mhc_layer_bwd (src/python/bindings.cu:330-401).
+ * out:  dx [B,n,C] dtype;  d_rmsnorm_weight [C], d_H_pre [n], d_H_post [n], d_H_res [n,n] fp32,
+ *       gradients w.r.t. the RAW parameters (through sigmoid / exp / Sinkhorn). */
+int mhc_static_bwd(void* dx, float* d_rmsnorm_weight, float* d_H_pre, float* d_H_post,
+                   float* d_H_res, const void* dy, const void* x, const void* rmsnorm_weight,
+                   const float* H_res, const float* rms, const float* H_pre_act,
+                   const float* H_post_act, const float* M, int64_t B, int n, int64_t C, int iters,
+                   float eps, int dtype, void* workspace, size_t workspace_bytes,
+                   mhc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Sinkhorn-Knopp on a batch of square fp32 matrices [batch, n, n], n <= 32: `iters` rounds of
+ * row then column normalisation, each dividing by (sum + eps).
+ * Replaces sinkhorn_knopp_fwd / sinkhorn_knopp_forward_batched
+ * (src/python/bindings.cu:115-121, src/csrc/kernels/sinkhorn_knopp.cuh:986-1046). */
+int mhc_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int n, int iters, float eps,
+                     mhc_stream_t stream);
+
+/* Exact gradient of mhc_sinkhorn_fwd w.r.t. its input, differentiating all 2*iters steps.
+ * Replaces sinkhorn_knopp_bwd (src/python/bindings.cu:123-132,
+ * src/csrc/kernels/sinkhorn_knopp.cuh:586-825). */
+int mhc_sinkhorn_bwd(float* d_inp, const float* grad_out, const float* inp, int64_t batch, int n,
+                     int iters, float eps, void* workspace, size_t workspace_bytes,
+                     mhc_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * RMSNorm over the last axis of a bf16 [B, C] tensor with a bf16 weight:
+ * out = inp / sqrt(mean(inp^2) + eps) * weight; rms [B] fp32 is saved for the backward.
+ * Replaces rmsnorm_fwd (src/python/bindings.cu:134-146). */
+int mhc_rmsnorm_fwd(void* out, float* rms, const void* inp, const void* weight, int64_t B,
+                    int64_t C, float eps, mhc_stream_t stream);
+
+/* RMSNorm backward: d_inp [B,C] bf16, d_weight [C] fp32 (written, summed over B in a fixed order).
+ * Replaces rmsnorm_bwd (src/python/bindings.cu:148-164). */
+int mhc_rmsnorm_bwd(void* d_inp, float* d_weight, const void* grad_out, const void* inp,
+                    const void* weight, const float* rms, int64_t B, int64_t C, void* workspace,
+                    size_t workspace_bytes, mhc_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MHC_B200_H_ */

@@ -1,0 +1,61 @@
+"""ctypes binding of libmhc_b200.so (the C ABI declared in include/mhc_b200.h).
+
+There is no fallback: if the shared object is missing or a call returns a non-zero status, a
+RuntimeError is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmhc_b200.so")
+
+F32, BF16 = 0, 1
+OP_DYNAMIC_FWD, OP_DYNAMIC_BWD, OP_STATIC_FWD, OP_STATIC_BWD = 0, 1, 2, 3
+OP_SINKHORN_FWD, OP_SINKHORN_BWD, OP_RMSNORM_FWD, OP_RMSNORM_BWD = 4, 5, 6, 7
+
+_p, _i, _l, _f, _z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/mhc_b200.h one to one
+SIGNATURES = {
+    "mhc_status_string": (C.c_char_p, [_i]),
+    "mhc_last_cuda_error": (C.c_char_p, []),
+    "mhc_abi_version": (_i, []),
+    "mhc_workspace_bytes": (_z, [_i, _l, _i, _l, _i, _i]),
+    "mhc_dynamic_fwd": (_i, [_p] * 12 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_dynamic_bwd": (_i, [_p] * 17 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_static_fwd": (_i, [_p] * 10 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_static_bwd": (_i, [_p] * 13 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_sinkhorn_fwd": (_i, [_p, _p, _l, _i, _i, _f, _p]),
+    "mhc_sinkhorn_bwd": (_i, [_p, _p, _p, _l, _i, _i, _f, _p, _z, _p]),
+    "mhc_rmsnorm_fwd": (_i, [_p, _p, _p, _p, _l, _l, _f, _p]),
+    "mhc_rmsnorm_bwd": (_i, [_p] * 6 + [_l, _l, _p, _z, _p]),
+}
+
+_lib = None
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m mhc.cu_b200.build` "
+                "(needs nvcc; there is no CPU or PyTorch fallback)")
+        h = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(h, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = h
+    return _lib
+
+
+def check(status, what):
+    if status != 0:
+        h = lib()
+        msg = h.mhc_status_string(status).decode()
+        if status == 7:
+            msg += ": " + h.mhc_last_cuda_error().decode()
+        raise RuntimeError(f"{what} failed with status {status}: {msg}")

@@ -1,0 +1,120 @@
+"""Builds the native pieces in-tree with nvcc / g++ for sm_100a.
+
+  libmhc_b200.so   the CUDA kernels behind the C ABI of include/mhc_b200.h (no torch dependency)
+  mhc_cuda*.so     the C++ torch extension that allocates outputs and forwards to the C ABI
+
+Usage:  python -m mhc.cu_b200.build [--force] [--no-ext]
+Objects go to mhc/cu_b200/build/ (git-ignored); the shared objects sit next to this file so that
+they are found without installation.
+"""
+from __future__ import annotations
+
+import argparse
+import concurrent.futures
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+ROOT = os.path.dirname(os.path.dirname(HERE))
+INCLUDE = os.path.join(ROOT, "include")
+OBJ = os.path.join(HERE, "build")
+LIB = os.path.join(HERE, "libmhc_b200.so")
+
+CU_SOURCES = ["coeffs.cu", "stream_ops.cu", "proj.cu", "rmsnorm.cu", "abi.cu"]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++20",
+              "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-I" + INCLUDE]
+
+
+def _nvcc():
+    return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def _newer(target, deps):
+    if not os.path.exists(target):
+        return False
+    t = os.path.getmtime(target)
+    return all(os.path.getmtime(d) <= t for d in deps)
+
+
+def _headers():
+    hs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    hs.append(os.path.join(INCLUDE, "mhc_b200.h"))
+    return hs
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build step failed:\n" + " ".join(cmd) + "\n" + r.stdout)
+    return r.stdout
+
+
+def build_lib(force=False, verbose=False):
+    srcs = [os.path.join(CSRC, s) for s in CU_SOURCES]
+    deps = srcs + _headers()
+    if not force and _newer(LIB, deps):
+        return LIB
+    os.makedirs(OBJ, exist_ok=True)
+    objs = [os.path.join(OBJ, os.path.basename(s)[:-3] + ".o") for s in srcs]
+
+    def one(pair):
+        src, obj = pair
+        if not force and _newer(obj, [src] + _headers()):
+            return
+        _run([_nvcc()] + NVCC_FLAGS + ["-c", src, "-o", obj], verbose)
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(srcs)) as ex:
+        list(ex.map(one, zip(srcs, objs)))
+    _run([_nvcc(), "-shared", "-o", LIB] + objs + ["-gencode", "arch=compute_100a,code=sm_100a"], verbose)
+    return LIB
+
+
+def ext_path():
+    return os.path.join(HERE, "mhc_cuda" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_ext(force=False, verbose=False):
+    """g++ the pybind11 torch extension and link it against libmhc_b200.so (rpath $ORIGIN)."""
+    src = os.path.join(CSRC, "torch_ext.cpp")
+    if not os.path.exists(src):
+        return None
+    out = ext_path()
+    if not force and _newer(out, [src, LIB, os.path.join(INCLUDE, "mhc_b200.h")]):
+        return out
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    inc = ["-I" + p for p in ce.include_paths()] + ["-I" + sysconfig.get_paths()["include"], "-I" + INCLUDE,
+                                                   "-I/usr/local/cuda/include"]
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-DTORCH_EXTENSION_NAME=mhc_cuda",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           src, "-o", out] + inc + [
+        "-L" + torch_lib, "-L" + HERE, "-lmhc_b200", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda",
+        "-ltorch", "-ltorch_python", "-L/usr/local/cuda/lib64", "-lcudart",
+        "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + torch_lib]
+    _run(cmd, verbose)
+    return out
+
+
+def build(force=False, verbose=False, ext=True):
+    build_lib(force, verbose)
+    if ext:
+        build_ext(force, verbose)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--force", action="store_true")
+    ap.add_argument("--no-ext", action="store_true")
+    ap.add_argument("-v", "--verbose", action="store_true")
+    a = ap.parse_args()
+    build(a.force, a.verbose, not a.no_ext)
+    print("built", LIB)
+    sys.exit(0)

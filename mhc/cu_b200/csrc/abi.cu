@@ -1,0 +1,373 @@
+// extern "C" entry points declared in include/mhc_b200.h: argument validation, workspace carving
+// and the kernel sequence of each call.  No allocation, no host synchronisation, no global state
+// besides a thread-local copy of the last CUDA error text.
+#include "../../../include/mhc_b200.h"
+
+#include <cstring>
+
+#include "kernels.h"
+
+namespace {
+
+using namespace mhc;
+
+thread_local char g_last_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t e) {
+    std::strncpy(g_last_cuda_error, cudaGetErrorString(e), sizeof(g_last_cuda_error) - 1);
+    g_last_cuda_error[sizeof(g_last_cuda_error) - 1] = '\0';
+    return MHC_ERR_CUDA;
+}
+
+#define MHC_TRY(expr)                                        \
+    do {                                                     \
+        cudaError_t e__ = (expr);                            \
+        if (e__ == cudaErrorNotSupported) return MHC_ERR_UNSUPPORTED; \
+        if (e__ != cudaSuccess) return cuda_fail(e__);       \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Bump allocator over the caller's workspace; with base == nullptr it only measures.
+struct Carver {
+    char* base;
+    size_t off = 0;
+    explicit Carver(void* b) : base(static_cast<char*>(b)) {}
+    void* take_bytes(size_t bytes) {
+        off = (off + 255) & ~size_t(255);
+        void* p = base ? base + off : nullptr;
+        off += bytes;
+        return p;
+    }
+    template <typename T>
+    T* take(size_t count) {
+        return static_cast<T*>(take_bytes(count * sizeof(T)));
+    }
+};
+
+int check_dims(int64_t B, int n, int64_t C, int iters, int dtype) {
+    if (dtype != MHC_F32 && dtype != MHC_BF16) return MHC_ERR_BAD_DTYPE;
+    if (B < 0 || B > 0x7fffffffLL || n < 1 || n > kMaxStreams || C < 1 || iters < 0)
+        return MHC_ERR_BAD_SHAPE;
+    if (C > (int64_t(1) << 40) / n) return MHC_ERR_BAD_SHAPE;
+    return MHC_OK;
+}
+
+size_t den_elem(int dtype) { return dtype == MHC_F32 ? sizeof(double) : sizeof(float); }
+
+struct DynFwdWs {
+    float* praw;
+    float* sumsq;
+    DynFwdWs(Carver& c, Dims d) {
+        praw = c.take<float>((size_t)d.B * d.K());
+        sumsq = c.take<float>((size_t)d.B);
+    }
+};
+
+struct DynBwdWs {
+    float *dH, *c2, *dpr, *qq, *partials, *dw_part;
+    void* den;
+    int nblk, ntb;
+    DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
+        nblk = coeffs_dyn_bwd_blocks(d);
+        ntb = dx_token_blocks(d);
+        dH = c.take<float>((size_t)d.B * d.K());
+        c2 = c.take<float>((size_t)d.B);
+        dpr = c.take<float>((size_t)d.B * d.K());
+        qq = c.take<float>((size_t)d.B);
+        partials = c.take<float>((size_t)nblk * (d.K() + 3));
+        dw_part = c.take<float>((size_t)ntb * d.C);
+        const int G = group_lanes(d.n) < 2 ? 2 : group_lanes(d.n);
+        den = c.take_bytes((size_t)d.B * G * 2 * (size_t)iters * den_elem(dtype));
+    }
+};
+
+struct StaticFwdWs {
+    float *hp, *hq, *M, *rms;
+    StaticFwdWs(Carver& c, Dims d) {
+        hp = c.take<float>(d.n);
+        hq = c.take<float>(d.n);
+        M = c.take<float>((size_t)d.n * d.n);
+        rms = c.take<float>((size_t)d.B);
+    }
+};
+
+struct StaticBwdWs {
+    float *dH, *c2, *dw_part;
+    void* den;
+    int ntb;
+    StaticBwdWs(Carver& c, Dims d, int iters, int dtype) {
+        ntb = dx_token_blocks(d);
+        dH = c.take<float>((size_t)d.B * d.K());
+        c2 = c.take<float>((size_t)d.B);
+        dw_part = c.take<float>((size_t)ntb * d.C);
+        den = c.take_bytes((size_t)32 * 2 * (size_t)iters * den_elem(dtype));
+    }
+};
+
+size_t sinkhorn_bwd_ws(int64_t batch, int n, int iters) {
+    const int G = group_lanes(n) < 2 ? 2 : group_lanes(n);
+    return (size_t)batch * G * 2 * (size_t)iters * sizeof(double);
+}
+
+template <typename T>
+int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+                  float* proj, const void* x, const void* w, const void* phi, const float* alpha,
+                  const float* bias, Dims d, int iters, float eps, int dtype, void* workspace,
+                  cudaStream_t s) {
+    Carver c(workspace);
+    DynFwdWs ws(c, d);
+    MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
+    MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, 1, alpha, bias,
+                                  d, iters, eps, dtype == MHC_F32, s));
+    MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1, d,
+                                eps, s));
+    return MHC_OK;
+}
+
+template <typename T>
+int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_bias, const void* dy,
+                  const void* x, const void* w, const void* phi, const float* alpha,
+                  const float* bias, const float* rms, const float* rms_h, const float* H_pre,
+                  const float* H_post, const float* M, const float* proj, Dims d, int iters,
+                  float eps, int dtype, void* workspace, cudaStream_t s) {
+    Carver c(workspace);
+    DynBwdWs ws(c, d, iters, dtype);
+    MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
+                                 H_post, 1, rms, d, s));
+    MHC_TRY(launch_coeffs_dyn_bwd(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
+                                  alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, s));
+    MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
+                             H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d, s));
+    MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+    MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials, ws.nblk,
+                            d.n, s));
+    return MHC_OK;
+}
+
+template <typename T>
+int static_fwd_t(void* y, float* rms, float* hp, float* hq, float* M, const void* x, const void* w,
+                 const float* H_pre, const float* H_post, const float* H_res, Dims d, int iters,
+                 float eps, int dtype, cudaStream_t s) {
+    MHC_TRY(launch_coeffs_static_fwd(hp, hq, M, H_pre, H_post, H_res, d.n, iters, eps,
+                                     dtype == MHC_F32, s));
+    MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, 0, d, eps, s));
+    return MHC_OK;
+}
+
+template <typename T>
+int static_bwd_t(void* dx, float* d_w, float* d_H_pre, float* d_H_post, float* d_H_res,
+                 const void* dy, const void* x, const void* w, const float* H_res, const float* rms,
+                 const float* hp, const float* hq, const float* M, Dims d, int iters, float eps,
+                 int dtype, void* workspace, cudaStream_t s) {
+    Carver c(workspace);
+    StaticBwdWs ws(c, d, iters, dtype);
+    MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq, 0,
+                                 rms, d, s));
+    MHC_TRY(launch_coeffs_static_bwd(d_H_pre, d_H_post, d_H_res, ws.dH, hp, hq, H_res, ws.den, d,
+                                     iters, eps, dtype == MHC_F32, s));
+    MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq,
+                             M, 0, rms, ws.c2, nullptr, nullptr, (const T*)nullptr, d, s));
+    MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, nullptr, nullptr, nullptr, 0, d.n, s));
+    return MHC_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mhc_status_string(int status) {
+    switch (status) {
+        case MHC_OK: return "ok";
+        case MHC_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case MHC_ERR_BAD_SHAPE: return "bad shape: need B >= 0, 1 <= n <= 32, C >= 1, iters >= 0";
+        case MHC_ERR_BAD_DTYPE: return "bad dtype tag (0 = fp32, 1 = bf16)";
+        case MHC_ERR_MISALIGNED: return "tensor or workspace pointer is not 16-byte aligned";
+        case MHC_ERR_WORKSPACE: return "workspace smaller than mhc_workspace_bytes() asks for";
+        case MHC_ERR_UNSUPPORTED: return "no kernel for this configuration in this build";
+        case MHC_ERR_CUDA: return "CUDA error (see mhc_last_cuda_error)";
+        case MHC_ERR_LIMIT: return "size beyond the fixed capacity of this entry point";
+        default: return "unknown status";
+    }
+}
+
+const char* mhc_last_cuda_error(void) { return g_last_cuda_error; }
+
+int mhc_abi_version(void) { return 1; }
+
+size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int dtype) {
+    const bool sk = (op == MHC_OP_SINKHORN_FWD || op == MHC_OP_SINKHORN_BWD);
+    const bool rn = (op == MHC_OP_RMSNORM_FWD || op == MHC_OP_RMSNORM_BWD);
+    if (rn) {
+        if (B < 0 || C < 1) return (size_t)-1;
+        if (op == MHC_OP_RMSNORM_FWD) return 0;
+        return (size_t)rmsnorm_bwd_blocks(B) * (size_t)C * sizeof(float) + 256;
+    }
+    if (check_dims(B, n, sk ? 1 : C, iters, sk ? MHC_F32 : dtype) != MHC_OK) return (size_t)-1;
+    const Dims d{B, n, sk ? 1 : C};
+    Carver c(nullptr);
+    switch (op) {
+        case MHC_OP_DYNAMIC_FWD: { DynFwdWs w(c, d); break; }
+        case MHC_OP_DYNAMIC_BWD: { DynBwdWs w(c, d, iters, dtype); break; }
+        case MHC_OP_STATIC_FWD: { StaticFwdWs w(c, d); break; }
+        case MHC_OP_STATIC_BWD: { StaticBwdWs w(c, d, iters, dtype); break; }
+        case MHC_OP_SINKHORN_FWD: return 0;
+        case MHC_OP_SINKHORN_BWD: return sinkhorn_bwd_ws(B, n, iters) + 256;
+        default: return (size_t)-1;
+    }
+    return c.off + 256;
+}
+
+int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+                    float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                    const float* alpha, const float* bias, int64_t B, int n, int64_t C, int iters,
+                    float eps, int dtype, void* workspace, size_t workspace_bytes,
+                    mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!y || !rms || !rms_h || !H_pre || !H_post || !M || !proj || !x || !rmsnorm_weight || !phi ||
+        !alpha || !bias)
+        return MHC_ERR_NULL_POINTER;
+    if (!aligned16(y) || !aligned16(x) || !aligned16(phi) || !aligned16(rmsnorm_weight) ||
+        !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = mhc_workspace_bytes(MHC_OP_DYNAMIC_FWD, B, n, C, iters, dtype);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    const Dims d{B, n, C};
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return dynamic_fwd_t<float>(y, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi,
+                                    alpha, bias, d, iters, eps, dtype, workspace, s);
+    return dynamic_fwd_t<bf16>(y, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi, alpha,
+                               bias, d, iters, eps, dtype, workspace, s);
+}
+
+int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha, float* d_bias,
+                    const void* dy, const void* x, const void* rmsnorm_weight, const void* phi,
+                    const float* alpha, const float* bias, const float* rms, const float* rms_h,
+                    const float* H_pre, const float* H_post, const float* M, const float* proj,
+                    int64_t B, int n, int64_t C, int iters, float eps, int dtype, void* workspace,
+                    size_t workspace_bytes, mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!dx || !d_rmsnorm_weight || !d_phi || !d_alpha || !d_bias || !dy || !x || !rmsnorm_weight ||
+        !phi || !alpha || !bias || !rms || !rms_h || !H_pre || !H_post || !M || !proj)
+        return MHC_ERR_NULL_POINTER;
+    if (!aligned16(dx) || !aligned16(dy) || !aligned16(x) || !aligned16(phi) || !aligned16(d_phi) ||
+        !aligned16(rmsnorm_weight) || !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = mhc_workspace_bytes(MHC_OP_DYNAMIC_BWD, B, n, C, iters, dtype);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    const Dims d{B, n, C};
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return dynamic_bwd_t<float>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, dy, x,
+                                    rmsnorm_weight, phi, alpha, bias, rms, rms_h, H_pre, H_post, M,
+                                    proj, d, iters, eps, dtype, workspace, s);
+    return dynamic_bwd_t<bf16>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, dy, x, rmsnorm_weight,
+                               phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj, d, iters, eps,
+                               dtype, workspace, s);
+}
+
+int mhc_static_fwd(void* y, float* rms, float* H_pre_act, float* H_post_act, float* M,
+                   const void* x, const void* rmsnorm_weight, const float* H_pre,
+                   const float* H_post, const float* H_res, int64_t B, int n, int64_t C, int iters,
+                   float eps, int dtype, void* workspace, size_t workspace_bytes,
+                   mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!y || !x || !rmsnorm_weight || !H_pre || !H_post || !H_res) return MHC_ERR_NULL_POINTER;
+    if (!aligned16(y) || !aligned16(x) || !aligned16(rmsnorm_weight) || !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const bool need_ws = (!rms || !H_pre_act || !H_post_act || !M);
+    const size_t need = mhc_workspace_bytes(MHC_OP_STATIC_FWD, B, n, C, iters, dtype);
+    if (need_ws && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    const Dims d{B, n, C};
+    if (need_ws) {
+        Carver c(workspace);
+        StaticFwdWs ws(c, d);
+        if (!H_pre_act) H_pre_act = ws.hp;
+        if (!H_post_act) H_post_act = ws.hq;
+        if (!M) M = ws.M;
+        if (!rms) rms = ws.rms;
+    }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return static_fwd_t<float>(y, rms, H_pre_act, H_post_act, M, x, rmsnorm_weight, H_pre,
+                                   H_post, H_res, d, iters, eps, dtype, s);
+    return static_fwd_t<bf16>(y, rms, H_pre_act, H_post_act, M, x, rmsnorm_weight, H_pre, H_post,
+                              H_res, d, iters, eps, dtype, s);
+}
+
+int mhc_static_bwd(void* dx, float* d_rmsnorm_weight, float* d_H_pre, float* d_H_post,
+                   float* d_H_res, const void* dy, const void* x, const void* rmsnorm_weight,
+                   const float* H_res, const float* rms, const float* H_pre_act,
+                   const float* H_post_act, const float* M, int64_t B, int n, int64_t C, int iters,
+                   float eps, int dtype, void* workspace, size_t workspace_bytes,
+                   mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!dx || !d_rmsnorm_weight || !d_H_pre || !d_H_post || !d_H_res || !dy || !x ||
+        !rmsnorm_weight || !H_res || !rms || !H_pre_act || !H_post_act || !M)
+        return MHC_ERR_NULL_POINTER;
+    if (!aligned16(dx) || !aligned16(dy) || !aligned16(x) || !aligned16(rmsnorm_weight) ||
+        !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = mhc_workspace_bytes(MHC_OP_STATIC_BWD, B, n, C, iters, dtype);
+    if (!workspace || workspace_bytes < need) return MHC_ERR_WORKSPACE;
+    const Dims d{B, n, C};
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return static_bwd_t<float>(dx, d_rmsnorm_weight, d_H_pre, d_H_post, d_H_res, dy, x,
+                                   rmsnorm_weight, H_res, rms, H_pre_act, H_post_act, M, d, iters,
+                                   eps, dtype, workspace, s);
+    return static_bwd_t<bf16>(dx, d_rmsnorm_weight, d_H_pre, d_H_post, d_H_res, dy, x,
+                              rmsnorm_weight, H_res, rms, H_pre_act, H_post_act, M, d, iters, eps,
+                              dtype, workspace, s);
+}
+
+int mhc_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int n, int iters, float eps,
+                     mhc_stream_t stream) {
+    if (int st = check_dims(batch, n, 1, iters, MHC_F32)) return st;
+    if (!out || !inp) return MHC_ERR_NULL_POINTER;
+    MHC_TRY(launch_sinkhorn_fwd(out, inp, batch, n, iters, eps,
+                                reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_sinkhorn_bwd(float* d_inp, const float* grad_out, const float* inp, int64_t batch, int n,
+                     int iters, float eps, void* workspace, size_t workspace_bytes,
+                     mhc_stream_t stream) {
+    if (int st = check_dims(batch, n, 1, iters, MHC_F32)) return st;
+    if (!d_inp || !grad_out || !inp) return MHC_ERR_NULL_POINTER;
+    if (!aligned16(workspace)) return MHC_ERR_MISALIGNED;
+    const size_t need = sinkhorn_bwd_ws(batch, n, iters);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    MHC_TRY(launch_sinkhorn_bwd(d_inp, grad_out, inp, workspace, batch, n, iters, eps,
+                                reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_rmsnorm_fwd(void* out, float* rms, const void* inp, const void* weight, int64_t B,
+                    int64_t C, float eps, mhc_stream_t stream) {
+    if (B < 0 || B > 0x7fffffffLL || C < 1) return MHC_ERR_BAD_SHAPE;
+    if (!out || !rms || !inp || !weight) return MHC_ERR_NULL_POINTER;
+    if (!aligned16(out) || !aligned16(inp) || !aligned16(weight)) return MHC_ERR_MISALIGNED;
+    MHC_TRY(launch_rmsnorm_fwd((bf16*)out, rms, (const bf16*)inp, (const bf16*)weight, B, C, eps,
+                               reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_rmsnorm_bwd(void* d_inp, float* d_weight, const void* grad_out, const void* inp,
+                    const void* weight, const float* rms, int64_t B, int64_t C, void* workspace,
+                    size_t workspace_bytes, mhc_stream_t stream) {
+    if (B < 0 || B > 0x7fffffffLL || C < 1) return MHC_ERR_BAD_SHAPE;
+    if (!d_inp || !d_weight || !grad_out || !inp || !weight || !rms) return MHC_ERR_NULL_POINTER;
+    if (!aligned16(d_inp) || !aligned16(grad_out) || !aligned16(inp) || !aligned16(weight) ||
+        !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = (size_t)rmsnorm_bwd_blocks(B) * (size_t)C * sizeof(float);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    MHC_TRY(launch_rmsnorm_bwd((bf16*)d_inp, d_weight, (float*)workspace, (const bf16*)grad_out,
+                               (const bf16*)inp, (const bf16*)weight, rms, B, C,
+                               reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,453 @@
+// Per-token small algebra of the mHC layer: RMS scaling of the projections, sigmoid / 2*sigmoid /
+// exp activations, Sinkhorn-Knopp forward, and the exact backward through all of it.
+//
+// Thread mapping: a group of G lanes (G = power of two >= n) owns one token; lane r of the group
+// owns row r of the n x n residual-mixing matrix (see sinkhorn.cuh).  256-thread blocks hold
+// 256/G tokens.  Token-summed gradients (d_bias, d_alpha) leave each block as one partial row that
+// finalize_kernel adds up in a fixed order, so results are bit-reproducible.
+//
+// Takes over fused_h_activations (src/csrc/include/utils.cuh:49-126), the batched Sinkhorn
+// kernels (src/csrc/kernels/sinkhorn_knopp.cuh:827-1046), sinkhorn_knopp_backward (same file,
+// 586-825) and the eager tail of the dynamic backward (src/python/mhc/ops.py:276-361) of the
+// reference.
+#include "kernels.h"
+#include "sinkhorn.cuh"
+
+namespace mhc {
+
+namespace {
+
+constexpr int kCoeffThreads = 256;
+
+template <typename A>
+__device__ __forceinline__ A root(A v);
+template <>
+__device__ __forceinline__ float root<float>(float v) { return sqrtf(v); }
+template <>
+__device__ __forceinline__ double root<double>(double v) { return sqrt(v); }
+
+// ------------------------------------------------------------------------------------------------
+// dynamic forward: praw[nsplit][B][K], sumsq[nsplit][B]  ->  rms_h, proj, H_pre, H_post, M
+template <int G, typename A>
+__global__ void __launch_bounds__(kCoeffThreads)
+coeffs_dyn_fwd_kernel(float* __restrict__ H_pre, float* __restrict__ H_post, float* __restrict__ M,
+                      float* __restrict__ proj, float* __restrict__ rms_h,
+                      const float* __restrict__ praw, const float* __restrict__ sumsq, int nsplit,
+                      const float* __restrict__ alpha, const float* __restrict__ bias, int64_t B,
+                      int n, int64_t nC, int iters, float eps) {
+    constexpr int GPB = kCoeffThreads / G;
+    const int grp = threadIdx.x / G;
+    const int lane_row = threadIdx.x % G;
+    const int64_t tok = (int64_t)blockIdx.x * GPB + grp;
+    const bool act = (tok < B) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    const int K = 2 * n + n * n;
+
+    A m[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) m[j] = A(0);
+
+    if (act) {
+        float ss = 0.f;
+        for (int s = 0; s < nsplit; ++s) ss += sumsq[(int64_t)s * B + tok];
+        const A r = root<A>(A(ss) / A(nC) + A(eps));
+        const A rinv = A(1) / r;
+        if (lane_row == 0) rms_h[tok] = (float)r;
+        const float* pr0 = praw + tok * K;
+        const int64_t sstride = B * K;
+        auto P = [&](int k) -> A {
+            float v = 0.f;
+            for (int s = 0; s < nsplit; ++s) v += pr0[(int64_t)s * sstride + k];
+            return A(v) * rinv;
+        };
+        float* pj = proj + tok * K;
+        const A pp = P(row), pq = P(n + row);
+        pj[row] = (float)pp;
+        pj[n + row] = (float)pq;
+        H_pre[tok * n + row] = (float)sk_sigmoid<A>(A(alpha[0]) * pp + A(bias[row]));
+        H_post[tok * n + row] = (float)(A(2) * sk_sigmoid<A>(A(alpha[1]) * pq + A(bias[n + row])));
+        const A a2 = A(alpha[2]);
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (j < n) {
+                const int k = 2 * n + row * n + j;
+                const A pv = P(k);
+                pj[k] = (float)pv;
+                m[j] = sk_exp<A>(a2 * pv + A(bias[k]));
+            }
+        }
+    }
+    sk_forward<G, A, false>(m, n, row, iters, A(eps), nullptr);
+    if (act) {
+        float* Mo = M + tok * n * n + row * n;
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) Mo[j] = (float)m[j];
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// dynamic backward: dH[B][K] (gradients w.r.t. H_pre, H_post, M)  ->  dpr = alpha*dt/r  [B][K],
+// qq [B] = sum_k dpr_k p_k / (nC r), and per-block partial sums of dt (-> d_bias) and dt*p
+// (-> d_alpha) in partials[block][K+3].
+template <int G, typename A>
+__global__ void __launch_bounds__(kCoeffThreads)
+coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __restrict__ partials,
+                      const float* __restrict__ dH, const float* __restrict__ H_pre,
+                      const float* __restrict__ H_post, const float* __restrict__ proj,
+                      const float* __restrict__ rms_h, const float* __restrict__ alpha,
+                      const float* __restrict__ bias, A* __restrict__ den_ws, int64_t B, int n,
+                      int64_t nC, int iters, float eps) {
+    extern __shared__ float sm[];  // [GPB][K+3]
+    constexpr int GPB = kCoeffThreads / G;
+    const int grp = threadIdx.x / G;
+    const int lane_row = threadIdx.x % G;
+    const int64_t tok = (int64_t)blockIdx.x * GPB + grp;
+    const bool act = (tok < B) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    const int K = 2 * n + n * n;
+    const int KP = K + 3;
+
+    for (int i = threadIdx.x; i < GPB * KP; i += kCoeffThreads) sm[i] = 0.f;
+    __syncthreads();
+
+    A y[G], d[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) { y[j] = A(0); d[j] = A(0); }
+
+    const A a0 = A(alpha[0]), a1 = A(alpha[1]), a2 = A(alpha[2]);
+    const float* pj = proj + (act ? tok : 0) * K;
+    const float* dh = dH + (act ? tok : 0) * K;
+    A* den = den_ws + ((act ? tok : 0) * G + lane_row) * 2 * (int64_t)iters;
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (j < n) {
+                const int k = 2 * n + row * n + j;
+                y[j] = sk_exp<A>(a2 * A(pj[k]) + A(bias[k]));
+                d[j] = A(dh[k]);
+            }
+        }
+    }
+    sk_forward<G, A, true>(y, n, row, iters, A(eps), den);
+    sk_backward<G, A>(d, y, n, row, iters, den);
+
+    A qacc = A(0), dal0 = A(0), dal1 = A(0), dal2 = A(0);
+    A r = A(1);
+    if (act) {
+        r = A(rms_h[tok]);
+        const A rinv = A(1) / r;
+        const A hp = A(H_pre[tok * n + row]), hq = A(H_post[tok * n + row]);
+        const A pp = A(pj[row]), pq = A(pj[n + row]);
+        const A dtp = A(dh[row]) * hp * (A(1) - hp);
+        const A dtq = A(dh[n + row]) * hq * (A(1) - hq * A(0.5));
+        const A vp = a0 * dtp * rinv, vq = a1 * dtq * rinv;
+        float* dpo = dpr + tok * K;
+        float* smg = sm + grp * KP;
+        dpo[row] = (float)vp;
+        dpo[n + row] = (float)vq;
+        smg[row] = (float)dtp;
+        smg[n + row] = (float)dtq;
+        qacc = vp * pp + vq * pq;
+        dal0 = dtp * pp;
+        dal1 = dtq * pq;
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (j < n) {
+                const int k = 2 * n + row * n + j;
+                const A dtr = d[j] * y[j];  // dE * E
+                const A pv = A(pj[k]);
+                const A v = a2 * dtr * rinv;
+                dpo[k] = (float)v;
+                smg[k] = (float)dtr;
+                qacc += v * pv;
+                dal2 += dtr * pv;
+            }
+        }
+    }
+    qacc = group_sum<G, A>(qacc);
+    dal0 = group_sum<G, A>(dal0);
+    dal1 = group_sum<G, A>(dal1);
+    dal2 = group_sum<G, A>(dal2);
+    if (act && lane_row == 0) {
+        qq[tok] = (float)(qacc / (A(nC) * r));
+        float* smg = sm + grp * KP;
+        smg[K] = (float)dal0;
+        smg[K + 1] = (float)dal1;
+        smg[K + 2] = (float)dal2;
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < KP; k += kCoeffThreads) {
+        float t = 0.f;
+        for (int g = 0; g < GPB; ++g) t += sm[g * KP + k];
+        partials[(int64_t)blockIdx.x * KP + k] = t;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// static forward: one set of coefficients.  Launched with one warp.
+template <int G, typename A>
+__global__ void coeffs_static_fwd_kernel(float* __restrict__ H_pre_act,
+                                         float* __restrict__ H_post_act, float* __restrict__ M,
+                                         const float* __restrict__ H_pre,
+                                         const float* __restrict__ H_post,
+                                         const float* __restrict__ H_res, int n, int iters,
+                                         float eps) {
+    const int lane_row = threadIdx.x % G;
+    const bool act = (threadIdx.x / G == 0) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    A m[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) m[j] = A(0);
+    if (act) {
+        H_pre_act[row] = (float)sk_sigmoid<A>(A(H_pre[row]));
+        H_post_act[row] = (float)(A(2) * sk_sigmoid<A>(A(H_post[row])));
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) m[j] = sk_exp<A>(A(H_res[row * n + j]));
+    }
+    sk_forward<G, A, false>(m, n, row, iters, A(eps), nullptr);
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) M[row * n + j] = (float)m[j];
+    }
+}
+
+// static backward: sums dH[B][K] over tokens (fixed order), then one group runs the Sinkhorn
+// backward and the activation derivatives.  One block of 1024 threads.
+template <int G, typename A>
+__global__ void __launch_bounds__(1024)
+coeffs_static_bwd_kernel(float* __restrict__ d_H_pre, float* __restrict__ d_H_post,
+                         float* __restrict__ d_H_res, const float* __restrict__ dH,
+                         const float* __restrict__ H_pre_act, const float* __restrict__ H_post_act,
+                         const float* __restrict__ H_res, A* __restrict__ den_ws, int64_t B, int n,
+                         int iters, float eps, int P, int TL) {
+    extern __shared__ float sm[];  // [TL][K] partial sums, then row 0 holds the totals
+    const int K = 2 * n + n * n;
+    const int e0 = threadIdx.x % P;
+    const int tl = threadIdx.x / P;
+    if (tl < TL) {
+        for (int e = e0; e < K; e += P) {
+            float t = 0.f;
+            for (int64_t b = tl; b < B; b += TL) t += dH[b * K + e];
+            sm[tl * K + e] = t;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < K; e += blockDim.x) {
+        float t = 0.f;
+        for (int l = 0; l < TL; ++l) t += sm[l * K + e];
+        sm[e] = t;  // thread e is the only reader of column e: no hazard
+    }
+    __syncthreads();
+    if (threadIdx.x >= 32) return;
+
+    const int lane_row = threadIdx.x % G;
+    const bool act = (threadIdx.x / G == 0) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    A y[G], d[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) { y[j] = A(0); d[j] = A(0); }
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (j < n) {
+                y[j] = sk_exp<A>(A(H_res[row * n + j]));
+                d[j] = A(sm[2 * n + row * n + j]);
+            }
+        }
+    }
+    A* den = den_ws + (int64_t)lane_row * 2 * iters;
+    sk_forward<G, A, true>(y, n, row, iters, A(eps), den);
+    sk_backward<G, A>(d, y, n, row, iters, den);
+    if (act) {
+        const A hp = A(H_pre_act[row]), hq = A(H_post_act[row]);
+        d_H_pre[row] = (float)(A(sm[row]) * hp * (A(1) - hp));
+        d_H_post[row] = (float)(A(sm[n + row]) * hq * (A(1) - hq * A(0.5)));
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) d_H_res[row * n + j] = (float)(d[j] * y[j]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// stand-alone batched Sinkhorn on [batch][n][n]
+template <int G, typename A>
+__global__ void __launch_bounds__(kCoeffThreads)
+sinkhorn_fwd_kernel(float* __restrict__ out, const float* __restrict__ inp, int64_t batch, int n,
+                    int iters, float eps) {
+    constexpr int GPB = kCoeffThreads / G;
+    const int lane_row = threadIdx.x % G;
+    const int64_t mat = (int64_t)blockIdx.x * GPB + threadIdx.x / G;
+    const bool act = (mat < batch) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    A m[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) m[j] = A(0);
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) m[j] = A(inp[mat * n * n + row * n + j]);
+    }
+    sk_forward<G, A, false>(m, n, row, iters, A(eps), nullptr);
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) out[mat * n * n + row * n + j] = (float)m[j];
+    }
+}
+
+template <int G, typename A>
+__global__ void __launch_bounds__(kCoeffThreads)
+sinkhorn_bwd_kernel(float* __restrict__ d_inp, const float* __restrict__ grad,
+                    const float* __restrict__ inp, A* __restrict__ den_ws, int64_t batch, int n,
+                    int iters, float eps) {
+    constexpr int GPB = kCoeffThreads / G;
+    const int lane_row = threadIdx.x % G;
+    const int64_t mat = (int64_t)blockIdx.x * GPB + threadIdx.x / G;
+    const bool act = (mat < batch) && (lane_row < n);
+    const int row = act ? lane_row : G;
+    A y[G], d[G];
+#pragma unroll
+    for (int j = 0; j < G; ++j) { y[j] = A(0); d[j] = A(0); }
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+            if (j < n) {
+                y[j] = A(inp[mat * n * n + row * n + j]);
+                d[j] = A(grad[mat * n * n + row * n + j]);
+            }
+        }
+    }
+    A* den = den_ws + ((act ? mat : 0) * G + lane_row) * 2 * (int64_t)iters;
+    sk_forward<G, A, true>(y, n, row, iters, A(eps), den);
+    sk_backward<G, A>(d, y, n, row, iters, den);
+    if (act) {
+#pragma unroll
+        for (int j = 0; j < G; ++j)
+            if (j < n) d_inp[mat * n * n + row * n + j] = (float)d[j];
+    }
+}
+
+// Calls f.template operator()<G>() with G = group_lanes(n).
+template <typename F>
+cudaError_t dispatch_group(int n, F&& f) {
+    switch (group_lanes(n)) {
+        case 1:
+        case 2: return f.template operator()<2>();
+        case 4: return f.template operator()<4>();
+        case 8: return f.template operator()<8>();
+        case 16: return f.template operator()<16>();
+        case 32: return f.template operator()<32>();
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+inline unsigned blocks_for(int64_t items, int G) {
+    const int gpb = kCoeffThreads / G;
+    return (unsigned)((items + gpb - 1) / gpb);
+}
+
+}  // namespace
+
+cudaError_t launch_coeffs_dyn_fwd(float* H_pre, float* H_post, float* M, float* proj, float* rms_h,
+                                  const float* praw, const float* sumsq, int nsplit,
+                                  const float* alpha, const float* bias, Dims d, int iters,
+                                  float eps, bool use_double, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    return dispatch_group(d.n, [&]<int G>() -> cudaError_t {
+        const unsigned grid = blocks_for(d.B, G);
+        if (use_double)
+            coeffs_dyn_fwd_kernel<G, double><<<grid, kCoeffThreads, 0, s>>>(
+                H_pre, H_post, M, proj, rms_h, praw, sumsq, nsplit, alpha, bias, d.B, d.n, d.nC(),
+                iters, eps);
+        else
+            coeffs_dyn_fwd_kernel<G, float><<<grid, kCoeffThreads, 0, s>>>(
+                H_pre, H_post, M, proj, rms_h, praw, sumsq, nsplit, alpha, bias, d.B, d.n, d.nC(),
+                iters, eps);
+        return cudaPeekAtLastError();
+    });
+}
+
+int coeffs_dyn_bwd_blocks(Dims d) { return (int)blocks_for(d.B, group_lanes(d.n) < 2 ? 2 : group_lanes(d.n)); }
+
+cudaError_t launch_coeffs_dyn_bwd(float* dpr, float* qq, float* partials, const float* dH,
+                                  const float* H_pre, const float* H_post, const float* proj,
+                                  const float* rms_h, const float* alpha, const float* bias,
+                                  void* den_ws, Dims d, int iters, float eps, bool use_double,
+                                  cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    return dispatch_group(d.n, [&]<int G>() -> cudaError_t {
+        const unsigned grid = blocks_for(d.B, G);
+        const size_t smem = (size_t)(kCoeffThreads / G) * (d.K() + 3) * sizeof(float);
+        if (use_double)
+            coeffs_dyn_bwd_kernel<G, double><<<grid, kCoeffThreads, smem, s>>>(
+                dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (double*)den_ws, d.B,
+                d.n, d.nC(), iters, eps);
+        else
+            coeffs_dyn_bwd_kernel<G, float><<<grid, kCoeffThreads, smem, s>>>(
+                dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (float*)den_ws, d.B,
+                d.n, d.nC(), iters, eps);
+        return cudaPeekAtLastError();
+    });
+}
+
+cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float* M,
+                                     const float* H_pre, const float* H_post, const float* H_res,
+                                     int n, int iters, float eps, bool use_double, cudaStream_t s) {
+    return dispatch_group(n, [&]<int G>() -> cudaError_t {
+        if (use_double)
+            coeffs_static_fwd_kernel<G, double><<<1, 32, 0, s>>>(H_pre_act, H_post_act, M, H_pre,
+                                                                 H_post, H_res, n, iters, eps);
+        else
+            coeffs_static_fwd_kernel<G, float><<<1, 32, 0, s>>>(H_pre_act, H_post_act, M, H_pre,
+                                                                H_post, H_res, n, iters, eps);
+        return cudaPeekAtLastError();
+    });
+}
+
+cudaError_t launch_coeffs_static_bwd(float* d_H_pre, float* d_H_post, float* d_H_res,
+                                     const float* dH, const float* H_pre_act,
+                                     const float* H_post_act, const float* H_res, void* den_ws,
+                                     Dims d, int iters, float eps, bool use_double, cudaStream_t s) {
+    const int K = d.K();
+    int P = 1;
+    while (P < K && P < 1024) P <<= 1;
+    const int TL = 1024 / P;
+    const size_t smem = (size_t)TL * K * sizeof(float);
+    return dispatch_group(d.n, [&]<int G>() -> cudaError_t {
+        if (use_double)
+            coeffs_static_bwd_kernel<G, double><<<1, 1024, smem, s>>>(
+                d_H_pre, d_H_post, d_H_res, dH, H_pre_act, H_post_act, H_res, (double*)den_ws, d.B,
+                d.n, iters, eps, P, TL);
+        else
+            coeffs_static_bwd_kernel<G, float><<<1, 1024, smem, s>>>(
+                d_H_pre, d_H_post, d_H_res, dH, H_pre_act, H_post_act, H_res, (float*)den_ws, d.B,
+                d.n, iters, eps, P, TL);
+        return cudaPeekAtLastError();
+    });
+}
+
+cudaError_t launch_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int n, int iters,
+                                float eps, cudaStream_t s) {
+    if (batch == 0) return cudaSuccess;
+    return dispatch_group(n, [&]<int G>() -> cudaError_t {
+        sinkhorn_fwd_kernel<G, float><<<blocks_for(batch, G), kCoeffThreads, 0, s>>>(
+            out, inp, batch, n, iters, eps);
+        return cudaPeekAtLastError();
+    });
+}
+
+cudaError_t launch_sinkhorn_bwd(float* d_inp, const float* grad, const float* inp, void* den_ws,
+                                int64_t batch, int n, int iters, float eps, cudaStream_t s) {
+    if (batch == 0) return cudaSuccess;
+    // fp64 arithmetic: the op is tiny and this keeps the 2*iters-step reverse sweep exact
+    return dispatch_group(n, [&]<int G>() -> cudaError_t {
+        sinkhorn_bwd_kernel<G, double><<<blocks_for(batch, G), kCoeffThreads, 0, s>>>(
+            d_inp, grad, inp, (double*)den_ws, batch, n, iters, eps);
+        return cudaPeekAtLastError();
+    });
+}
+
+}  // namespace mhc

@@ -1,0 +1,133 @@
+// Shared device helpers: 16-byte vector I/O in fp32 registers, warp / block reductions.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mhc {
+
+constexpr int kMaxStreams = 32;  // n, the expansion rate, is limited to 1..32
+
+typedef __nv_bfloat16 bf16;
+
+// Elements of T in one 16-byte vector.
+template <typename T>
+struct VecWidth;
+template <>
+struct VecWidth<float> {
+    static constexpr int value = 4;
+};
+template <>
+struct VecWidth<bf16> {
+    static constexpr int value = 8;
+};
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// load V consecutive elements starting at p into fp32 registers.  V is either the 16-byte vector
+// width of T (p must be 16-byte aligned) or 1.
+template <int V>
+__device__ __forceinline__ void load_vec(const float* __restrict__ p, float (&v)[V]) {
+    if constexpr (V == 4) {
+        float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = p[e];
+    }
+}
+template <int V>
+__device__ __forceinline__ void load_vec(const bf16* __restrict__ p, float (&v)[V]) {
+    if constexpr (V == 8) {
+        uint4 t = *reinterpret_cast<const uint4*>(p);
+        v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x);
+        v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+        v[4] = bf16_lo(t.z); v[5] = bf16_hi(t.z);
+        v[6] = bf16_lo(t.w); v[7] = bf16_hi(t.w);
+    } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = __bfloat162float(p[e]);
+    }
+}
+
+template <int V>
+__device__ __forceinline__ void store_vec(float* __restrict__ p, const float (&v)[V]) {
+    if constexpr (V == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) p[e] = v[e];
+    }
+}
+template <int V>
+__device__ __forceinline__ void store_vec(bf16* __restrict__ p, const float (&v)[V]) {
+    if constexpr (V == 8) {
+        uint4 t;
+        t.x = pack_bf16x2(v[0], v[1]);
+        t.y = pack_bf16x2(v[2], v[3]);
+        t.z = pack_bf16x2(v[4], v[5]);
+        t.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(p) = t;
+    } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) p[e] = __float2bfloat16_rn(v[e]);
+    }
+}
+
+// The RMSNorm weight is always bf16 (the layer keeps it as a bf16 parameter).
+template <int V>
+__device__ __forceinline__ void load_weight(const bf16* __restrict__ w, int64_t c, float (&v)[V]) {
+    if constexpr (V == 8) {
+        load_vec<8>(w + c, v);
+    } else if constexpr (V == 4) {
+        uint2 t = *reinterpret_cast<const uint2*>(w + c);
+        v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x);
+        v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
+    } else {
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = __bfloat162float(w[c + e]);
+    }
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Sum NV per-thread values over the whole block.  `scratch` holds NV * 32 floats of shared
+// memory.  On return every thread of warp 0 has the totals in v[]; other warps hold garbage.
+// All threads of the block must call it.  blockDim.x is a multiple of 32.
+template <int NV>
+__device__ __forceinline__ void block_sum(float (&v)[NV], float* scratch) {
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int nwarps = blockDim.x >> 5;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) v[k] = warp_sum(v[k]);
+    if (nwarps == 1) return;
+    __syncthreads();  // scratch may still be read from a previous use
+    if (lane == 0) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) scratch[k * 32 + warp] = v[k];
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+            float t = (lane < nwarps) ? scratch[k * 32 + lane] : 0.f;
+            v[k] = warp_sum(t);
+        }
+    }
+}
+
+// Runtime-length variant for larger value counts: values live in shared memory as
+// part[value][thread]; not used on the hot path.
+
+}  // namespace mhc

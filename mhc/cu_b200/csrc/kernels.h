@@ -1,0 +1,90 @@
+// Host-side launchers of the kernels, one per .cu file.  Each returns the cudaError_t of its
+// launch (cudaPeekAtLastError) and never synchronises.  The C ABI in abi.cu validates arguments,
+// carves the workspace and sequences these.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace mhc {
+
+// Shapes shared by most launchers.
+struct Dims {
+    int64_t B;  // tokens
+    int n;      // streams
+    int64_t C;  // hidden
+    int K() const { return 2 * n + n * n; }
+    int64_t nC() const { return (int64_t)n * C; }
+};
+
+// Smallest power of two >= n (n in 1..32): lanes per Sinkhorn group.
+inline int group_lanes(int n) {
+    int g = 1;
+    while (g < n) g <<= 1;
+    return g;
+}
+
+// ---- coeffs.cu: per-token small algebra (activations, Sinkhorn forward / backward) ------------
+// use_double selects fp64 arithmetic for the per-token algebra (the fp32 I/O path).
+cudaError_t launch_coeffs_dyn_fwd(float* H_pre, float* H_post, float* M, float* proj, float* rms_h,
+                                  const float* praw, const float* sumsq, int nsplit,
+                                  const float* alpha, const float* bias, Dims d, int iters,
+                                  float eps, bool use_double, cudaStream_t s);
+// den_ws: B * G * 2 * iters elements of float / double.  partials: [blocks][K+3]; returns the
+// number of blocks through *nblocks (callable with all pointers NULL to query it).
+int coeffs_dyn_bwd_blocks(Dims d);
+cudaError_t launch_coeffs_dyn_bwd(float* dpr, float* qq, float* partials, const float* dH,
+                                  const float* H_pre, const float* H_post, const float* proj,
+                                  const float* rms_h, const float* alpha, const float* bias,
+                                  void* den_ws, Dims d, int iters, float eps, bool use_double,
+                                  cudaStream_t s);
+cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float* M,
+                                     const float* H_pre, const float* H_post, const float* H_res,
+                                     int n, int iters, float eps, bool use_double, cudaStream_t s);
+cudaError_t launch_coeffs_static_bwd(float* d_H_pre, float* d_H_post, float* d_H_res,
+                                     const float* dH, const float* H_pre_act,
+                                     const float* H_post_act, const float* H_res, void* den_ws,
+                                     Dims d, int iters, float eps, bool use_double, cudaStream_t s);
+cudaError_t launch_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int n, int iters,
+                                float eps, cudaStream_t s);
+cudaError_t launch_sinkhorn_bwd(float* d_inp, const float* grad, const float* inp, void* den_ws,
+                                int64_t batch, int n, int iters, float eps, cudaStream_t s);
+
+// ---- stream_ops.cu: the passes over the [B,n,C] streams ---------------------------------------
+template <typename T>
+cudaError_t launch_apply_fwd(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                             const float* H_post, const float* M, int coef_stride, Dims d,
+                             float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_bwd_reduce(float* dH, float* c2, const T* x, const T* g, const bf16* w,
+                              const float* H_pre, const float* H_post, int coef_stride,
+                              const float* rms, Dims d, cudaStream_t s);
+// tokens handled by one block of the dx pass (its dw partials are [dx_token_blocks][C])
+int dx_token_blocks(Dims d);
+template <typename T>
+cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
+                          const float* H_pre, const float* H_post, const float* M,
+                          int coef_stride, const float* rms, const float* c2, const float* dpr,
+                          const float* qq, const T* phi, Dims d, cudaStream_t s);
+cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
+                            float* d_alpha, const float* partials, int nparts2, int n,
+                            cudaStream_t s);
+
+// ---- proj.cu: the two contractions against phi that reduce over columns / tokens --------------
+template <typename T>
+cudaError_t launch_proj(float* praw, float* sumsq, const T* x, const T* phi, Dims d,
+                        cudaStream_t s);
+template <typename T>
+cudaError_t launch_dphi(float* dphi, const T* x, const float* dpr, Dims d, cudaStream_t s);
+
+// ---- rmsnorm.cu --------------------------------------------------------------------------------
+cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,
+                               int64_t C, float eps, cudaStream_t s);
+int rmsnorm_bwd_blocks(int64_t B);
+cudaError_t launch_rmsnorm_bwd(bf16* d_inp, float* d_w, float* dw_part, const bf16* grad,
+                               const bf16* inp, const bf16* w, const float* rms, int64_t B,
+                               int64_t C, cudaStream_t s);
+
+}  // namespace mhc

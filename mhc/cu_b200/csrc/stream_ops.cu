@@ -1,0 +1,497 @@
+// The passes over the [B, n, C] residual streams (n <= 8): everything here is HBM-bound and moves
+// 16-byte vectors; per-token coefficients sit in registers.
+//
+//   apply_fwd   y[i,:] = sum_j M[i,j] x[j,:] + H_post[i] * rmsnorm(sum_i H_pre[i] x[i,:]) * w
+//               One block per token; the token's n rows stay in registers between the sum-of-squares
+//               sweep and the output sweep, so x is read once and y written once.
+//   bwd_reduce  all per-token inner products the backward needs, from one read of x and dy.
+//   bwd_dx      dx, element-wise given the per-token scalars; also the column sums for d_weight.
+//
+// Takes over stream_aggregate_bf16_dynamic / rmsnorm_forward_with_rms /
+// stream_distribute_mix_add_fused_dynamic (src/csrc/kernels/stream_ops.cuh:451-642,
+// src/csrc/kernels/rmsnorm.cuh:13-232), their static variants (stream_ops.cuh:26-217,332-449) and
+// the backward kernels (stream_ops.cuh:644-997, rmsnorm.cuh:233-306) of the reference, including
+// per-token coefficients in the backward, which the reference's dynamic path lacks
+// (it indexes M / H_post / H_pre without a batch offset, stream_ops.cuh:767-770).
+#include "kernels.h"
+
+namespace mhc {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// forward
+template <typename T, int V, int MAXN, int VPT, int MAXT>
+__global__ void __launch_bounds__(MAXT)
+apply_fwd_kernel(T* __restrict__ y, float* __restrict__ rho_out, const T* __restrict__ x,
+                 const bf16* __restrict__ w, const float* __restrict__ H_pre,
+                 const float* __restrict__ H_post, const float* __restrict__ M, int coef_stride,
+                 int n, int64_t C, float eps) {
+    __shared__ float red[32];
+    __shared__ float rho_inv_s;
+    const int64_t b = blockIdx.x;
+    const int64_t nvec = C / V;
+    const T* xb = x + b * n * C;
+    T* yb = y + b * n * C;
+    const int64_t cb = b * coef_stride;
+
+    float hp[MAXN], hq[MAXN], m[MAXN][MAXN];
+#pragma unroll
+    for (int i = 0; i < MAXN; ++i) {
+        hp[i] = 0.f;
+        hq[i] = 0.f;
+        if (i < n) {
+            hp[i] = H_pre[cb * n + i];
+            hq[i] = H_post[cb * n + i];
+        }
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) m[i][j] = (i < n && j < n) ? M[cb * n * n + i * n + j] : 0.f;
+    }
+
+    constexpr int NCACHE = VPT > 0 ? VPT : 1;
+    float xr[NCACHE][MAXN][V];
+    float ss = 0.f;
+    if constexpr (VPT > 0) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int64_t v = threadIdx.x + (int64_t)k * blockDim.x;
+            if (v < nvec) {
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i)
+                    if (i < n) load_vec<V>(xb + i * C + v * V, xr[k][i]);
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float a = 0.f;
+#pragma unroll
+                    for (int i = 0; i < MAXN; ++i)
+                        if (i < n) a = fmaf(hp[i], xr[k][i][e], a);
+                    ss = fmaf(a, a, ss);
+                }
+            }
+        }
+    } else {
+        for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i)
+                if (i < n) load_vec<V>(xb + i * C + v * V, xr[0][i]);
+#pragma unroll
+            for (int e = 0; e < V; ++e) {
+                float a = 0.f;
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i)
+                    if (i < n) a = fmaf(hp[i], xr[0][i][e], a);
+                ss = fmaf(a, a, ss);
+            }
+        }
+    }
+    float tot[1] = {ss};
+    block_sum<1>(tot, red);
+    if (threadIdx.x == 0) {
+        const float rho = sqrtf(tot[0] / (float)C + eps);
+        rho_out[b] = rho;
+        rho_inv_s = 1.f / rho;
+    }
+    __syncthreads();
+    const float ri = rho_inv_s;
+
+    auto emit = [&](int64_t v, float (&xv)[MAXN][V]) {
+        float wv[V], yn[V];
+        load_weight<V>(w, v * V, wv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i)
+                if (i < n) a = fmaf(hp[i], xv[i][e], a);
+            yn[e] = a * ri * wv[e];
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                float o[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float t = hq[i] * yn[e];
+#pragma unroll
+                    for (int j = 0; j < MAXN; ++j)
+                        if (j < n) t = fmaf(m[i][j], xv[j][e], t);
+                    o[e] = t;
+                }
+                store_vec<V>(yb + i * C + v * V, o);
+            }
+        }
+    };
+
+    if constexpr (VPT > 0) {
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int64_t v = threadIdx.x + (int64_t)k * blockDim.x;
+            if (v < nvec) emit(v, xr[k]);
+        }
+    } else {
+        for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i)
+                if (i < n) load_vec<V>(xb + i * C + v * V, xr[0][i]);
+            emit(v, xr[0]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, pass A: per-token inner products.
+//   s      = <u, a>            u = w * sum_i H_post[i] g[i,:],  a = sum_i H_pre[i] x[i,:]
+//   dM[i,j]= <g[i,:], x[j,:]>
+//   dH_post[i] = <g[i,:], a*w> / rho
+//   dH_pre[i]  = <da, x[i,:]>  with da = u/rho - a*s/(C rho^3)   ( = <u,x_i>/rho - c2 <a,x_i> )
+// Output dH[b][K] in projection order (pre, post, res) and c2[b] = s / (C rho^3).
+template <typename T, int V, int MAXN>
+__global__ void __launch_bounds__(256)
+bwd_reduce_kernel(float* __restrict__ dH, float* __restrict__ c2_out, const T* __restrict__ x,
+                  const T* __restrict__ g, const bf16* __restrict__ w,
+                  const float* __restrict__ H_pre, const float* __restrict__ H_post,
+                  int coef_stride, const float* __restrict__ rms, int n, int64_t C) {
+    constexpr int NR = 1 + MAXN * MAXN + 3 * MAXN;
+    __shared__ float red[NR * 32];
+    const int64_t b = blockIdx.x;
+    const int64_t nvec = C / V;
+    const T* xb = x + b * n * C;
+    const T* gb = g + b * n * C;
+    const int64_t cb = b * coef_stride;
+
+    float hp[MAXN], hq[MAXN];
+#pragma unroll
+    for (int i = 0; i < MAXN; ++i) {
+        hp[i] = (i < n) ? H_pre[cb * n + i] : 0.f;
+        hq[i] = (i < n) ? H_post[cb * n + i] : 0.f;
+    }
+    float acc[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) acc[k] = 0.f;
+    // acc layout: [0] s | [1 .. 1+MAXN^2) dM | then P[MAXN] | ux[MAXN] | ax[MAXN]
+    constexpr int OM = 1, OP = 1 + MAXN * MAXN, OU = OP + MAXN, OA = OU + MAXN;
+
+    for (int64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float xv[MAXN][V], gv[MAXN][V], wv[V];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                load_vec<V>(xb + i * C + v * V, xv[i]);
+                load_vec<V>(gb + i * C + v * V, gv[i]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) { xv[i][e] = 0.f; gv[i][e] = 0.f; }
+            }
+        }
+        load_weight<V>(w, v * V, wv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float a = 0.f, dyh = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) {
+                a = fmaf(hp[i], xv[i][e], a);
+                dyh = fmaf(hq[i], gv[i][e], dyh);
+            }
+            const float u = dyh * wv[e];
+            const float aw = a * wv[e];
+            acc[0] = fmaf(u, a, acc[0]);
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) {
+                acc[OP + i] = fmaf(gv[i][e], aw, acc[OP + i]);
+                acc[OU + i] = fmaf(u, xv[i][e], acc[OU + i]);
+                acc[OA + i] = fmaf(a, xv[i][e], acc[OA + i]);
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    acc[OM + i * MAXN + j] = fmaf(gv[i][e], xv[j][e], acc[OM + i * MAXN + j]);
+            }
+        }
+    }
+    block_sum<NR>(acc, red);
+    if (threadIdx.x == 0) {
+        const float ri = 1.f / rms[b];
+        const float c2 = acc[0] * ri * ri * ri / (float)C;
+        c2_out[b] = c2;
+        const int K = 2 * n + n * n;
+        float* o = dH + b * K;
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                o[i] = ri * acc[OU + i] - c2 * acc[OA + i];
+                o[n + i] = acc[OP + i] * ri;
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    if (j < n) o[2 * n + i * n + j] = acc[OM + i * MAXN + j];
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// backward, pass B: dx.  Block = 32 column vectors x 8 token lanes; a block walks kDxTokens tokens.
+//   dx[j,:] = sum_i M[i,j] g[i,:] + H_pre[j] da            da = u/rho - a*c2
+//           + (sum_k dpr_k phi_k[j,:]) - x[j,:] * qq       (dynamic-H only)
+//   dw_part[block_y][c] = sum over the block's tokens of (sum_i H_post[i] g[i,c]) * a[c] / rho
+constexpr int kDxTokens = 32;
+constexpr int kDxTY = 8;
+
+template <typename T, int V, int MAXN, bool DYNAMIC>
+__global__ void __launch_bounds__(256)
+bwd_dx_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restrict__ x,
+              const T* __restrict__ g, const bf16* __restrict__ w, const float* __restrict__ H_pre,
+              const float* __restrict__ H_post, const float* __restrict__ M, int coef_stride,
+              const float* __restrict__ rms, const float* __restrict__ c2,
+              const float* __restrict__ dpr, const float* __restrict__ qq,
+              const T* __restrict__ phi, int64_t B, int n, int64_t C) {
+    __shared__ float dws[kDxTY][32][V];
+    const int tx = threadIdx.x, ty = threadIdx.y;
+    const int64_t nvec = C / V;
+    const int64_t v = (int64_t)blockIdx.x * 32 + tx;
+    const bool colact = v < nvec;
+    const int64_t c0 = v * V;
+    const int64_t b0 = (int64_t)blockIdx.y * kDxTokens;
+    const int64_t b1 = (b0 + kDxTokens < B) ? b0 + kDxTokens : B;
+    const int K = 2 * n + n * n;
+    const int64_t nC = (int64_t)n * C;
+
+    float wv[V], dwacc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) { wv[e] = 0.f; dwacc[e] = 0.f; }
+    if (colact) load_weight<V>(w, c0, wv);
+
+    for (int64_t b = b0 + ty; b < b1; b += kDxTY) {
+        if (!colact) continue;
+        const int64_t cb = b * coef_stride;
+        float hp[MAXN], hq[MAXN], m[MAXN][MAXN];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            hp[i] = (i < n) ? H_pre[cb * n + i] : 0.f;
+            hq[i] = (i < n) ? H_post[cb * n + i] : 0.f;
+#pragma unroll
+            for (int j = 0; j < MAXN; ++j)
+                m[i][j] = (i < n && j < n) ? M[cb * n * n + i * n + j] : 0.f;
+        }
+        const float ri = 1.f / rms[b];
+        const float c2b = c2[b];
+        const T* xb = x + b * nC + c0;
+        const T* gb = g + b * nC + c0;
+        float xv[MAXN][V], gv[MAXN][V];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                load_vec<V>(xb + i * C, xv[i]);
+                load_vec<V>(gb + i * C, gv[i]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) { xv[i][e] = 0.f; gv[i][e] = 0.f; }
+            }
+        }
+        float da[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float a = 0.f, dyh = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) {
+                a = fmaf(hp[i], xv[i][e], a);
+                dyh = fmaf(hq[i], gv[i][e], dyh);
+            }
+            da[e] = dyh * wv[e] * ri - a * c2b;
+            dwacc[e] = fmaf(dyh * ri, a, dwacc[e]);
+        }
+        float qb = 0.f;
+        if constexpr (DYNAMIC) qb = qq[b];
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) {
+            if (j < n) {
+                float o[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float t = hp[j] * da[e];
+#pragma unroll
+                    for (int i = 0; i < MAXN; ++i) t = fmaf(m[i][j], gv[i][e], t);
+                    if constexpr (DYNAMIC) t = fmaf(-qb, xv[j][e], t);
+                    o[e] = t;
+                }
+                if constexpr (DYNAMIC) {
+                    const float* dp = dpr + b * K;
+                    const T* ph = phi + j * C + c0;
+                    for (int k = 0; k < K; ++k) {
+                        float pv[V];
+                        load_vec<V>(ph + (int64_t)k * nC, pv);
+                        const float dk = dp[k];
+#pragma unroll
+                        for (int e = 0; e < V; ++e) o[e] = fmaf(dk, pv[e], o[e]);
+                    }
+                }
+                store_vec<V>(dx + b * nC + j * C + c0, o);
+            }
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) dws[ty][tx][e] = dwacc[e];
+    __syncthreads();
+    if (ty == 0 && colact) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float t = 0.f;
+#pragma unroll
+            for (int l = 0; l < kDxTY; ++l) t += dws[l][tx][e];
+            dw_part[(int64_t)blockIdx.y * C + c0 + e] = t;
+        }
+    }
+}
+
+// d_w[c] = sum_parts dw_part[p][c];  d_bias[k], d_alpha[0..2] = sums of partials[p][K+3].
+__global__ void finalize_kernel(float* __restrict__ d_w, const float* __restrict__ dw_part,
+                                int nparts, int64_t C, float* __restrict__ d_bias,
+                                float* __restrict__ d_alpha, const float* __restrict__ partials,
+                                int nparts2, int K) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < C) {
+        float t = 0.f;
+        for (int p = 0; p < nparts; ++p) t += dw_part[(int64_t)p * C + i];
+        d_w[i] = t;
+    }
+    if (d_bias != nullptr && i < K + 3) {
+        float t = 0.f;
+        for (int p = 0; p < nparts2; ++p) t += partials[(int64_t)p * (K + 3) + i];
+        if (i < K)
+            d_bias[i] = t;
+        else
+            d_alpha[i - K] = t;
+    }
+}
+
+template <typename T>
+constexpr int vec_of() {
+    return VecWidth<T>::value;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------
+template <typename T, int V, int MAXN>
+static cudaError_t apply_fwd_pick(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                                  const float* H_post, const float* M, int coef_stride, Dims d,
+                                  float eps, cudaStream_t s) {
+    // at most 128 cached floats per thread (VPT * MAXN * V), 256 threads per block
+    constexpr int MAXT = 256;
+    constexpr int MAXVPT = (MAXN * V * 4 <= 128) ? 4 : 2;
+    const int64_t nvec = d.C / V;
+    auto round32 = [](int64_t t) { return (int)((t + 31) / 32 * 32); };
+    const unsigned grid = (unsigned)d.B;
+#define MHC_APPLY(VPT_, THREADS_)                                                                  \
+    apply_fwd_kernel<T, V, MAXN, VPT_, MAXT><<<grid, THREADS_, 0, s>>>(y, rho, x, w, H_pre, H_post, \
+                                                                       M, coef_stride, d.n, d.C, eps)
+    if (nvec <= MAXT) {
+        MHC_APPLY(1, round32(nvec));
+    } else if (MAXVPT >= 2 && nvec <= 2 * (int64_t)MAXT) {
+        MHC_APPLY((MAXVPT >= 2 ? 2 : 1), round32((nvec + 1) / 2));
+    } else if (MAXVPT >= 4 && nvec <= 4 * (int64_t)MAXT) {
+        MHC_APPLY((MAXVPT >= 4 ? 4 : 1), round32((nvec + 3) / 4));
+    } else {
+        MHC_APPLY(0, MAXT);
+    }
+#undef MHC_APPLY
+    return cudaPeekAtLastError();
+}
+
+template <typename T>
+cudaError_t launch_apply_fwd(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                             const float* H_post, const float* M, int coef_stride, Dims d,
+                             float eps, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (d.n > 8) return cudaErrorNotSupported;
+    constexpr int VW = vec_of<T>();
+    const bool vec = (d.C % VW == 0);
+    if (d.n <= 4) {
+        return vec ? apply_fwd_pick<T, VW, 4>(y, rho, x, w, H_pre, H_post, M, coef_stride, d, eps, s)
+                   : apply_fwd_pick<T, 1, 4>(y, rho, x, w, H_pre, H_post, M, coef_stride, d, eps, s);
+    }
+    return vec ? apply_fwd_pick<T, VW, 8>(y, rho, x, w, H_pre, H_post, M, coef_stride, d, eps, s)
+               : apply_fwd_pick<T, 1, 8>(y, rho, x, w, H_pre, H_post, M, coef_stride, d, eps, s);
+}
+
+template <typename T>
+cudaError_t launch_bwd_reduce(float* dH, float* c2, const T* x, const T* g, const bf16* w,
+                              const float* H_pre, const float* H_post, int coef_stride,
+                              const float* rms, Dims d, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (d.n > 8) return cudaErrorNotSupported;
+    constexpr int VW = vec_of<T>();
+    const bool vec = (d.C % VW == 0);
+    const int64_t nvec = vec ? d.C / VW : d.C;
+    int threads = (int)((nvec + 31) / 32 * 32);
+    if (threads > 256) threads = 256;
+    const unsigned grid = (unsigned)d.B;
+#define MHC_RED(V_, MAXN_)                                                                         \
+    bwd_reduce_kernel<T, V_, MAXN_><<<grid, threads, 0, s>>>(dH, c2, x, g, w, H_pre, H_post,        \
+                                                             coef_stride, rms, d.n, d.C)
+    if (d.n <= 4) {
+        if (vec) MHC_RED(VW, 4); else MHC_RED(1, 4);
+    } else {
+        if (vec) MHC_RED(VW, 8); else MHC_RED(1, 8);
+    }
+#undef MHC_RED
+    return cudaPeekAtLastError();
+}
+
+int dx_token_blocks(Dims d) { return (int)((d.B + kDxTokens - 1) / kDxTokens); }
+
+template <typename T>
+cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
+                          const float* H_pre, const float* H_post, const float* M,
+                          int coef_stride, const float* rms, const float* c2, const float* dpr,
+                          const float* qq, const T* phi, Dims d, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (d.n > 8) return cudaErrorNotSupported;
+    constexpr int VW = vec_of<T>();
+    const bool vec = (d.C % VW == 0);
+    const int64_t nvec = vec ? d.C / VW : d.C;
+    const dim3 block(32, kDxTY);
+    const dim3 grid((unsigned)((nvec + 31) / 32), (unsigned)dx_token_blocks(d));
+    const bool dyn = (phi != nullptr);
+#define MHC_DX(V_, MAXN_, DYN_)                                                                    \
+    bwd_dx_kernel<T, V_, MAXN_, DYN_><<<grid, block, 0, s>>>(dx, dw_part, x, g, w, H_pre, H_post,   \
+                                                             M, coef_stride, rms, c2, dpr, qq, phi, \
+                                                             d.B, d.n, d.C)
+#define MHC_DX2(V_, MAXN_)                                                                         \
+    do {                                                                                           \
+        if (dyn) MHC_DX(V_, MAXN_, true); else MHC_DX(V_, MAXN_, false);                           \
+    } while (0)
+    if (d.n <= 4) {
+        if (vec) MHC_DX2(VW, 4); else MHC_DX2(1, 4);
+    } else {
+        if (vec) MHC_DX2(VW, 8); else MHC_DX2(1, 8);
+    }
+#undef MHC_DX2
+#undef MHC_DX
+    return cudaPeekAtLastError();
+}
+
+cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
+                            float* d_alpha, const float* partials, int nparts2, int n,
+                            cudaStream_t s) {
+    const int K = 2 * n + n * n;
+    int64_t items = C > K + 3 ? C : K + 3;
+    const unsigned grid = (unsigned)((items + 255) / 256);
+    finalize_kernel<<<grid, 256, 0, s>>>(d_w, dw_part, nparts, C, d_bias, d_alpha, partials, nparts2,
+                                         K);
+    return cudaPeekAtLastError();
+}
+
+#define MHC_INSTANTIATE(T)                                                                         \
+    template cudaError_t launch_apply_fwd<T>(T*, float*, const T*, const bf16*, const float*,      \
+                                             const float*, const float*, int, Dims, float,         \
+                                             cudaStream_t);                                        \
+    template cudaError_t launch_bwd_reduce<T>(float*, float*, const T*, const T*, const bf16*,     \
+                                              const float*, const float*, int, const float*, Dims, \
+                                              cudaStream_t);                                       \
+    template cudaError_t launch_bwd_dx<T>(T*, float*, const T*, const T*, const bf16*,             \
+                                          const float*, const float*, const float*, int,           \
+                                          const float*, const float*, const float*, const float*,  \
+                                          const T*, Dims, cudaStream_t);
+MHC_INSTANTIATE(float)
+MHC_INSTANTIATE(bf16)
+#undef MHC_INSTANTIATE
+
+}  // namespace mhc

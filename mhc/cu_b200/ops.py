@@ -1,0 +1,200 @@
+"""autograd Functions and functional wrappers with the reference's names and argument order
+(src/python/mhc/ops.py of AndreSlavescu/mHC.cu), running on the sm_100a kernels.
+
+Differences from the reference, all deliberate:
+  * bf16 ``x`` stays bf16 end to end (the reference up-casts every input to fp32 and returns fp32,
+    ops.py:404 / bindings.cu:462); fp32 ``x`` gives fp32 ``y`` exactly as before, other dtypes are
+    computed in fp32.
+  * alpha stays on the device (no ``.item()`` synchronisation, ops.py:178-188) and the packed /
+    cast copy of phi is cached per parameter version instead of being rebuilt every call
+    (ops.py:172-177).
+  * the backward is exact and runs entirely in kernels (no per-token Python loop, ops.py:309-316).
+"""
+from __future__ import annotations
+
+import weakref
+
+import torch
+from torch.autograd import Function
+
+from . import capi
+
+_PACK_CACHE: dict = {}
+_PACK_CACHE_MAX = 16
+
+
+def _key(*tensors):
+    return tuple((t.data_ptr(), t._version, t.dtype, tuple(t.shape)) for t in tensors)
+
+
+def pack_phi(phi_pre, phi_post, phi_res, dtype):
+    """[K, nC] concatenation (pre, post, res) of the three projection matrices in ``dtype``.
+    Cached on (storage, version) so an unchanged parameter set is packed once."""
+    key = (_key(phi_pre, phi_post, phi_res), dtype)
+    hit = _PACK_CACHE.get(key)
+    if hit is not None:
+        packed, refs = hit
+        # an address can be handed out again once its tensor is gone: the entry only counts while
+        # the tensors it was packed from are still alive
+        if all(r() is t for r, t in zip(refs, (phi_pre, phi_post, phi_res))):
+            return packed
+        del _PACK_CACHE[key]
+    nC = phi_pre.shape[-1]
+    with torch.no_grad():
+        packed = torch.cat([phi_pre.reshape(-1, nC), phi_post.reshape(-1, nC), phi_res.reshape(-1, nC)],
+                           dim=0).to(dtype).contiguous()
+    if len(_PACK_CACHE) >= _PACK_CACHE_MAX:
+        _PACK_CACHE.pop(next(iter(_PACK_CACHE)))
+    _PACK_CACHE[key] = (packed, tuple(weakref.ref(t) for t in (phi_pre, phi_post, phi_res)))
+    return packed
+
+
+def _compute_dtype(x):
+    return torch.bfloat16 if x.dtype == torch.bfloat16 else torch.float32
+
+
+class SinkhornKnoppFunction(Function):
+    @staticmethod
+    def forward(ctx, inp, num_iters, eps):
+        inp = inp.contiguous()
+        out = capi.sinkhorn_fwd(inp, num_iters, eps)
+        ctx.save_for_backward(inp)
+        ctx.num_iters = num_iters
+        ctx.eps = eps
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (inp,) = ctx.saved_tensors
+        d_inp = capi.sinkhorn_bwd(grad_output.contiguous().float(), inp, ctx.num_iters, ctx.eps)
+        return d_inp, None, None
+
+
+class RMSNormFunction(Function):
+    @staticmethod
+    def forward(ctx, inp, weight, eps):
+        inp = inp.contiguous()
+        weight = weight.contiguous()
+        out, rms = capi.rmsnorm_fwd(inp, weight, eps)
+        ctx.save_for_backward(inp, weight, rms)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        inp, weight, rms = ctx.saved_tensors
+        d_inp, d_weight = capi.rmsnorm_bwd(grad_output.contiguous().bfloat16(), inp, weight, rms)
+        return d_inp, d_weight.to(weight.dtype), None
+
+
+def sinkhorn_knopp(inp, num_iters=20, eps=1e-8):
+    return SinkhornKnoppFunction.apply(inp.float(), num_iters, eps)
+
+
+def rmsnorm(inp, weight, eps=1e-5):
+    return RMSNormFunction.apply(inp.bfloat16(), weight.bfloat16(), eps)
+
+
+class MHCLayerFunction(Function):
+    """Static-H layer.  apply(x, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters, eps)."""
+
+    @staticmethod
+    def forward(ctx, x_expanded, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters, eps):
+        x = x_expanded.contiguous()
+        w = rmsnorm_weight.contiguous()
+        H_res = H_res.contiguous()
+        y, saved = capi.static_fwd(x, w, H_pre.contiguous(), H_post.contiguous(), H_res,
+                                   sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, H_res, saved["rms"], saved["H_pre_act"], saved["H_post_act"],
+                              saved["M"])
+        ctx.sinkhorn_iters = sinkhorn_iters
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w, H_res, rms, hp, hq, M = ctx.saved_tensors
+        saved = {"rms": rms, "H_pre_act": hp, "H_post_act": hq, "M": M}
+        dx, g = capi.static_bwd(grad_output.contiguous().to(x.dtype), x, w, H_res, saved,
+                                ctx.sinkhorn_iters, ctx.eps)
+        return (dx, g["d_rmsnorm_weight"].to(w.dtype), g["d_H_pre"], g["d_H_post"], g["d_H_res"],
+                None, None)
+
+
+def mhc_layer_fused(x_expanded, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters=20, eps=1e-5):
+    return MHCLayerFunction.apply(
+        x_expanded.to(_compute_dtype(x_expanded)), rmsnorm_weight.bfloat16(), H_pre.float(),
+        H_post.float(), H_res.float(), sinkhorn_iters, eps)
+
+
+def mhc_layer_fused_inference(x_expanded, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters=20,
+                              eps=1e-5):
+    """Forward only; nothing is saved for a backward pass."""
+    x = x_expanded.to(_compute_dtype(x_expanded)).contiguous()
+    y, _ = capi.static_fwd(x, rmsnorm_weight.bfloat16().contiguous(), H_pre.float().contiguous(),
+                           H_post.float().contiguous(), H_res.float().contiguous(), sinkhorn_iters,
+                           eps, inference=True)
+    return y
+
+
+class MHCLayerDynamicFunction(Function):
+    """Dynamic-H layer.  apply(x, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post,
+    alpha_res, b_pre, b_post, b_res, sinkhorn_iters, eps) -> y; backward returns the 11 gradients
+    and two None, in that order."""
+
+    @staticmethod
+    def forward(ctx, x_expanded, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post,
+                alpha_res, b_pre, b_post, b_res, sinkhorn_iters, eps):
+        x = x_expanded.contiguous()
+        w = rmsnorm_weight.contiguous()
+        n = phi_pre.size(0)
+        phi = pack_phi(phi_pre, phi_post, phi_res, x.dtype)
+        dev = x.device
+        alpha = torch.stack([torch.as_tensor(a, dtype=torch.float32, device=dev).reshape(())
+                             for a in (alpha_pre, alpha_post, alpha_res)]).float()
+        bias = torch.cat([b_pre.reshape(-1), b_post.reshape(-1), b_res.reshape(-1)]).float()
+        y, s = capi.dynamic_fwd(x, w, phi, alpha, bias, sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, phi, alpha, bias, s["rms"], s["rms_h"], s["H_pre"], s["H_post"],
+                              s["M"], s["proj"])
+        ctx.sinkhorn_iters = sinkhorn_iters
+        ctx.eps = eps
+        ctx.n = n
+        ctx.param_dtypes = (w.dtype, phi_pre.dtype, phi_post.dtype, phi_res.dtype,
+                            getattr(alpha_pre, "dtype", torch.float32),
+                            getattr(alpha_post, "dtype", torch.float32),
+                            getattr(alpha_res, "dtype", torch.float32),
+                            b_pre.dtype, b_post.dtype, b_res.dtype)
+        ctx.b_res_shape = tuple(b_res.shape)
+        ctx.phi_res_shape = tuple(phi_res.shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj = ctx.saved_tensors
+        saved = {"rms": rms, "rms_h": rms_h, "H_pre": H_pre, "H_post": H_post, "M": M, "proj": proj}
+        dx, g = capi.dynamic_bwd(grad_output.contiguous().to(x.dtype), x, w, phi, alpha, bias, saved,
+                                 ctx.sinkhorn_iters, ctx.eps)
+        n = ctx.n
+        dt = ctx.param_dtypes
+        d_phi, d_alpha, d_bias = g["d_phi"], g["d_alpha"], g["d_bias"]
+        return (dx, g["d_rmsnorm_weight"].to(dt[0]),
+                d_phi[:n].to(dt[1]), d_phi[n:2 * n].to(dt[2]),
+                d_phi[2 * n:].reshape(ctx.phi_res_shape).to(dt[3]),
+                d_alpha[0].to(dt[4]), d_alpha[1].to(dt[5]), d_alpha[2].to(dt[6]),
+                d_bias[:n].to(dt[7]), d_bias[n:2 * n].to(dt[8]),
+                d_bias[2 * n:].reshape(ctx.b_res_shape).to(dt[9]), None, None)
+
+
+def mhc_layer_fused_dynamic(x_expanded, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre,
+                            alpha_post, alpha_res, b_pre, b_post, b_res, sinkhorn_iters=20,
+                            eps=1e-5):
+    dev, pdt = phi_pre.device, phi_pre.dtype
+    if not torch.is_tensor(alpha_pre):
+        alpha_pre = torch.tensor(alpha_pre, device=dev, dtype=pdt)
+    if not torch.is_tensor(alpha_post):
+        alpha_post = torch.tensor(alpha_post, device=dev, dtype=pdt)
+    if not torch.is_tensor(alpha_res):
+        alpha_res = torch.tensor(alpha_res, device=dev, dtype=pdt)
+    return MHCLayerDynamicFunction.apply(
+        x_expanded.to(_compute_dtype(x_expanded)), rmsnorm_weight.bfloat16(), phi_pre.float(),
+        phi_post.float(), phi_res.float(), alpha_pre, alpha_post, alpha_res, b_pre.float(),
+        b_post.float(), b_res.float(), sinkhorn_iters, eps)

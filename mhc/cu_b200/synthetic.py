@@ -1,0 +1,79 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the benchmark
+configurations (no dataset is involved: the reference benchmarks on ``torch.randn`` too,
+src/python/benchmarks/bench_layer.py:148-232).
+
+  c1  static-H,  fp32, x [320, 4, 1280]
+  c2  dynamic-H, bf16, x [512, 4, 1920]
+  c3  dynamic-H, bf16, x [1280, 4, 2560]      (the headline shape)
+  c4  dynamic-H, bf16, x [128, 32, 1280]      (wide expansion)
+Everything is drawn on the CPU in fp32 from one generator, so every rank / device sees the
+same numbers for a given seed.
+"""
+from __future__ import annotations
+
+import torch
+
+CONFIGS = {
+    "c1": dict(kind="static", B=320, n=4, C=1280, dtype=torch.float32, eps=1e-5, iters=20),
+    "c2": dict(kind="dynamic", B=512, n=4, C=1920, dtype=torch.bfloat16, eps=1e-6, iters=20),
+    "c3": dict(kind="dynamic", B=1280, n=4, C=2560, dtype=torch.bfloat16, eps=1e-6, iters=20),
+    "c4": dict(kind="dynamic", B=128, n=32, C=1280, dtype=torch.bfloat16, eps=1e-6, iters=20),
+}
+
+
+def dynamic_params(n, C, seed=0, alpha=0.01, bias_scale=0.0, random_weight=False):
+    """Parameters shaped like ``MHCLayer(use_dynamic_h=True)``: phi ~ N(0, 0.02), alpha scalars,
+    zero (or small random) biases, unit (or random, bf16-exact) RMSNorm weight."""
+    g = torch.Generator().manual_seed(seed)
+    nC = n * C
+    w = torch.ones(C)
+    if random_weight:
+        w = (1.0 + 0.25 * torch.randn(C, generator=g)).bfloat16().float()
+    return {
+        "rmsnorm_weight": w,
+        "phi_pre": torch.randn(n, nC, generator=g) * 0.02,
+        "phi_post": torch.randn(n, nC, generator=g) * 0.02,
+        "phi_res": torch.randn(n * n, nC, generator=g) * 0.02,
+        "alpha_pre": torch.tensor(float(alpha)),
+        "alpha_post": torch.tensor(float(alpha)),
+        "alpha_res": torch.tensor(float(alpha)),
+        "b_pre": torch.randn(n, generator=g) * bias_scale,
+        "b_post": torch.randn(n, generator=g) * bias_scale,
+        "b_res": torch.randn(n, n, generator=g) * bias_scale,
+    }
+
+
+def static_params(n, C, seed=0, random_weight=False):
+    """Raw static-H parameters ~ N(0, 1); the layer applies sigmoid / 2*sigmoid / Sinkhorn(exp)."""
+    g = torch.Generator().manual_seed(seed)
+    w = torch.ones(C)
+    if random_weight:
+        w = (1.0 + 0.25 * torch.randn(C, generator=g)).bfloat16().float()
+    return {
+        "rmsnorm_weight": w,
+        "H_pre": torch.randn(n, generator=g),
+        "H_post": torch.randn(n, generator=g),
+        "H_res": torch.randn(n, n, generator=g),
+    }
+
+
+def streams(B, n, C, seed=0):
+    """x and dy ~ N(0, 1), fp32 on the CPU."""
+    g = torch.Generator().manual_seed(seed + 7919)
+    return torch.randn(B, n, C, generator=g), torch.randn(B, n, C, generator=g)
+
+
+def pack_dynamic(params, dtype, device):
+    """(rmsnorm_weight bf16 [C], phi [K,nC] dtype, alpha fp32 [3], bias fp32 [K]) on ``device``,
+    the packed form the C ABI takes."""
+    n = params["phi_pre"].shape[0]
+    nC = params["phi_pre"].shape[1]
+    phi = torch.cat([params["phi_pre"], params["phi_post"], params["phi_res"].reshape(n * n, nC)], 0)
+    alpha = torch.stack([params["alpha_pre"].reshape(()), params["alpha_post"].reshape(()),
+                         params["alpha_res"].reshape(())])
+    bias = torch.cat([params["b_pre"].reshape(-1), params["b_post"].reshape(-1),
+                      params["b_res"].reshape(-1)])
+    return (params["rmsnorm_weight"].to(device=device, dtype=torch.bfloat16).contiguous(),
+            phi.to(device=device, dtype=dtype).contiguous(),
+            alpha.to(device=device, dtype=torch.float32).contiguous(),
+            bias.to(device=device, dtype=torch.float32).contiguous())

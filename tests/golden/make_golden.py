@@ -39,6 +39,11 @@ def _randn(gen, *shape, scale=1.0, shift=0.0):
     return (torch.randn(*shape, generator=gen, dtype=torch.float32) * scale + shift).double()
 
 
+def _bf16_exact(t):
+    """The layer keeps rmsnorm_weight as a bf16 parameter: use values bf16 can hold exactly."""
+    return t.float().bfloat16().double()
+
+
 def _save(name, arrays):
     out = {k: (v.detach().numpy() if torch.is_tensor(v) else np.asarray(v)) for k, v in arrays.items()}
     np.savez_compressed(os.path.join(HERE, name + ".npz"), **out)
@@ -50,7 +55,7 @@ def dynamic_case(ref_fn, name, seed, B, n, C, iters, eps, alpha, bias_scale, w_r
     nC = n * C
     leaves = {
         "x": _randn(gen, B, n, C),
-        "rmsnorm_weight": _randn(gen, C, scale=0.25, shift=1.0) if w_random else torch.ones(C).double(),
+        "rmsnorm_weight": _bf16_exact(_randn(gen, C, scale=0.25, shift=1.0)) if w_random else torch.ones(C).double(),
         "phi_pre": _randn(gen, n, nC, scale=0.02),
         "phi_post": _randn(gen, n, nC, scale=0.02),
         "phi_res": _randn(gen, n * n, nC, scale=0.02),
@@ -101,7 +106,7 @@ def static_case(cls, name, seed, B, n, C, iters, eps):
         layer.H_pre.copy_(_randn(gen, n))
         layer.H_post.copy_(_randn(gen, n))
         layer.H_res.copy_(_randn(gen, n, n))
-        layer.rmsnorm_weight.copy_(_randn(gen, C, scale=0.25, shift=1.0))
+        layer.rmsnorm_weight.copy_(_bf16_exact(_randn(gen, C, scale=0.25, shift=1.0)))
     x = _randn(gen, B, n, C).requires_grad_(True)
     dy = _randn(gen, B, n, C)
     y = layer(x)

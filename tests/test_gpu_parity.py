@@ -1,0 +1,175 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.
+
+Tolerances (max|a-b| / max|b| per tensor): 1e-5 for fp32 streams, 2e-2 for bf16 streams, for y and
+for every input and parameter gradient.  The oracle is evaluated in fp64 on exactly the values the
+kernels consume (inputs rounded to the stream dtype), see gpu_common.oracle_inputs.
+"""
+import pytest
+import torch
+
+import oracle
+from gpu_common import TOL, oracle_inputs, run_dynamic, run_static
+from helpers import DYN_PARAMS, STATIC_PARAMS, assert_rel, golden_names, load_golden, rel_err
+from mhc.cu_b200 import capi, synthetic
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+_ids = {torch.float32: "fp32", torch.bfloat16: "bf16"}
+
+
+def _check(out, ref, keys, tol):
+    errs = {k: rel_err(out[k], ref[k]) for k in keys}
+    bad = {k: v for k, v in errs.items() if not v <= tol}
+    assert not bad, f"beyond {tol:.0e}: {bad}; all: {errs}"
+
+
+def _golden_small(prefix):
+    return [n for n in golden_names(prefix) if int(n.split("_n")[1].split("_")[0]) <= 8]
+
+
+@pytest.mark.parametrize("name", _golden_small("dyn"))
+def test_dynamic_golden_fp32(name):
+    """fp32 streams against the vectors drawn from the reference's naive layer."""
+    g = load_golden(name)
+    params = {k: g[k] for k in DYN_PARAMS}
+    out, _ = run_dynamic(g["x"], g["dy"], params, g["iters"], g["eps"], torch.float32)
+    _check(out, g, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], 1e-5)
+
+
+@pytest.mark.parametrize("name", _golden_small("static"))
+def test_static_golden_fp32(name):
+    g = load_golden(name)
+    params = {k: g[k] for k in STATIC_PARAMS}
+    out, _ = run_static(g["x"], g["dy"], params, g["iters"], g["eps"], torch.float32)
+    _check(out, g, ["y", "dx"] + ["d" + k for k in STATIC_PARAMS], 1e-5)
+
+
+DYN_SHAPES = [
+    # B, n, C, alpha, bias_scale
+    (1, 4, 16, 0.01, 0.0),
+    (3, 4, 64, 0.5, 0.3),
+    (17, 4, 136, 0.5, 0.3),
+    (64, 4, 256, 0.3, 0.2),
+    (33, 4, 2560, 0.2, 0.1),
+    (5, 2, 40, 0.5, 0.3),
+    (4, 3, 24, 0.5, 0.3),
+    (6, 8, 64, 0.4, 0.2),
+    (2, 5, 48, 0.4, 0.2),
+    (7, 4, 100, 0.5, 0.3),   # C not a multiple of the 16-byte vector for bf16
+    (3, 4, 6, 0.5, 0.3),     # nor for fp32
+    (40, 4, 4104, 0.3, 0.1),  # more column vectors than one block caches
+]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=_ids.get)
+@pytest.mark.parametrize("B,n,C,alpha,bs", DYN_SHAPES)
+def test_dynamic_seeded(B, n, C, alpha, bs, dtype):
+    params = synthetic.dynamic_params(n, C, seed=B + n + C, alpha=alpha, bias_scale=bs, random_weight=True)
+    x, dy = synthetic.streams(B, n, C, seed=1)
+    out, _ = run_dynamic(x, dy, params, 20, 1e-5, dtype)
+    xo, dyo, po = oracle_inputs(x, dy, params, dtype)
+    ref = oracle.dynamic_fwd_bwd(xo, po, dyo, 20, 1e-5, dtype=torch.float64)
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], TOL[dtype])
+
+
+STATIC_SHAPES = [(1, 4, 16), (8, 4, 128), (32, 4, 128), (17, 4, 136), (320, 4, 1280), (6, 8, 64),
+                 (5, 3, 40), (7, 4, 100), (3, 4, 6)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=_ids.get)
+@pytest.mark.parametrize("B,n,C", STATIC_SHAPES)
+def test_static_seeded(B, n, C, dtype):
+    params = synthetic.static_params(n, C, seed=B + C, random_weight=True)
+    x, dy = synthetic.streams(B, n, C, seed=2)
+    out, _ = run_static(x, dy, params, 20, 1e-5, dtype)
+    xo, dyo, po = oracle_inputs(x, dy, params, dtype, stream_rounded=())
+    ref = oracle.static_fwd_bwd(xo, po, dyo, 20, 1e-5, dtype=torch.float64)
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in STATIC_PARAMS], TOL[dtype])
+
+
+@pytest.mark.parametrize("cfg", ["c2", "c3"])
+def test_dynamic_full_size(cfg):
+    """The benchmark configurations at full size: parity with the fp64 oracle, and the
+    size-independent properties (doubly stochastic M; tokens independent of their neighbours)."""
+    c = synthetic.CONFIGS[cfg]
+    B, n, C, dtype = c["B"], c["n"], c["C"], c["dtype"]
+    params = synthetic.dynamic_params(n, C, seed=0)
+    x, dy = synthetic.streams(B, n, C, seed=0)
+    out, saved = run_dynamic(x, dy, params, c["iters"], c["eps"], dtype)
+    xo, dyo, po = oracle_inputs(x, dy, params, dtype)
+    ref = oracle.dynamic_fwd_bwd(xo, po, dyo, c["iters"], c["eps"], dtype=torch.float64)
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], TOL[dtype])
+    M = saved["M"].double().cpu()
+    assert float((M.sum(-1) - 1).abs().max()) <= 1e-5
+    assert float((M.sum(-2) - 1).abs().max()) <= 1e-5
+    assert bool((M >= 0).all())
+    # a token's output does not depend on which batch it sits in
+    sub = slice(B // 2, B // 2 + 5)
+    out2, _ = run_dynamic(x[sub], dy[sub], params, c["iters"], c["eps"], dtype)
+    assert torch.equal(out2["y"], out["y"][sub])
+    assert torch.equal(out2["dx"], out["dx"][sub])
+
+
+def test_static_full_size_c1():
+    c = synthetic.CONFIGS["c1"]
+    B, n, C, dtype = c["B"], c["n"], c["C"], c["dtype"]
+    params = synthetic.static_params(n, C, seed=0)
+    x, dy = synthetic.streams(B, n, C, seed=0)
+    out, saved = run_static(x, dy, params, c["iters"], c["eps"], dtype)
+    xo, dyo, po = oracle_inputs(x, dy, params, dtype, stream_rounded=())
+    ref = oracle.static_fwd_bwd(xo, po, dyo, c["iters"], c["eps"], dtype=torch.float64)
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in STATIC_PARAMS], TOL[dtype])
+    # loss = y.sum() as in the reference benchmark (bench_layer.py:187-232)
+    ones = torch.ones_like(dy)
+    out1, _ = run_static(x, ones, params, c["iters"], c["eps"], dtype)
+    ref1 = oracle.static_fwd_bwd(xo, po, ones.double(), c["iters"], c["eps"], dtype=torch.float64)
+    _check(out1, ref1, ["dx"] + ["d" + k for k in STATIC_PARAMS], TOL[dtype])
+
+
+def test_backward_is_linear_in_dy():
+    """dx and the parameter gradients are linear in dy (size-independent property)."""
+    B, n, C = 96, 4, 512
+    params = synthetic.dynamic_params(n, C, seed=3, alpha=0.3, bias_scale=0.1)
+    x, dy1 = synthetic.streams(B, n, C, seed=3)
+    _, dy2 = synthetic.streams(B, n, C, seed=4)
+    a, _ = run_dynamic(x, dy1, params, 20, 1e-5, torch.float32)
+    b, _ = run_dynamic(x, dy2, params, 20, 1e-5, torch.float32)
+    c, _ = run_dynamic(x, dy1 + 2 * dy2, params, 20, 1e-5, torch.float32)
+    for k in ["dx", "dphi_res", "drmsnorm_weight", "db_res", "dalpha_pre"]:
+        assert_rel(c[k], a[k] + 2 * b[k], 2e-5, k)
+
+
+def test_repeatable():
+    """Same inputs, same bits: the token-summed gradients use fixed-order reductions."""
+    B, n, C = 200, 4, 512
+    params = synthetic.dynamic_params(n, C, seed=5, alpha=0.3)
+    x, dy = synthetic.streams(B, n, C, seed=5)
+    a, _ = run_dynamic(x, dy, params, 20, 1e-5, torch.bfloat16)
+    b, _ = run_dynamic(x, dy, params, 20, 1e-5, torch.bfloat16)
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+
+
+def test_empty_batch():
+    n, C = 4, 64
+    params = synthetic.dynamic_params(n, C, seed=6)
+    x = torch.zeros(0, n, C)
+    out, _ = run_dynamic(x, x.clone(), params, 20, 1e-5, torch.float32)
+    assert out["y"].shape == (0, n, C)
+    assert float(out["dphi_res"].abs().max()) == 0.0
+    assert float(out["drmsnorm_weight"].abs().max()) == 0.0
+
+
+def test_extreme_scales_finite():
+    """x * 100 and x * 0.001 stay finite (src/python/tests/test_layer.py:273-287 of the reference)."""
+    B, n, C = 8, 4, 128
+    params = synthetic.dynamic_params(n, C, seed=7)
+    x, dy = synthetic.streams(B, n, C, seed=7)
+    for s in (100.0, 1e-3):
+        for dtype in DTYPES:
+            out, _ = run_dynamic(x * s, dy, params, 20, 1e-5, dtype)
+            assert all(bool(torch.isfinite(v).all()) for v in out.values())
+            sp = synthetic.static_params(n, C, seed=7)
+            out, _ = run_static(x * s, dy, sp, 20, 1e-5, dtype)
+            assert all(bool(torch.isfinite(v).all()) for v in out.values())
