@@ -1,0 +1,429 @@
+#!/usr/bin/env python3
+"""Benchmark of the mHC layer forward + backward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c3]
+
+One step = one forward + backward of the dynamic-H mHC layer over one batch of synthetic
+tokens (default workload c3: x [1280, 4, 2560] bf16 per GPU, phi ~ N(0, 0.02), alpha 0.01, eps 1e-6,
+20 Sinkhorn iterations).  With N > 1 (launched by torchrun, one rank per GPU) every rank works on
+its own batch of the same size (weak scaling) and the flat fp32 parameter-gradient bucket is
+all-reduced with NCCL inside the step.  Rank 0 prints ONE JSON line.
+
+  value      tokens/s over all ranks, inputs resident in HBM, K steps timed with CUDA events between
+             barrier+synchronize pairs, max over ranks.  Steps rotate over several input sets so the
+             working set exceeds the L2 cache.  The kernels of a step are replayed from a CUDA graph
+             (the C-ABI calls captured once), so host launch overhead is not in the number.
+  e2e        same metric through the public ``mhc.MHCLayer`` autograd API with x and dy coming from
+             pinned host memory and y, dx and the parameter gradients copied back every step.
+  roofline   algorithmic HBM bytes of one step / measured step time, against the measured copy
+             bandwidth in MEASURED_PEAKS.json (fallback 6650 GB/s).
+  cpu_baseline  the naive PyTorch layer (oracle/) timed on this box's host cores (N = 1 only).
+
+``--impl reference`` times that naive CPU layer itself as the reference arm.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "mHC layer fwd+bwd tokens/s (dynamic-H, bf16, B=1280 n=4 C=2560 per GPU)"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(B, n, C, io_bytes, phi_bytes):
+    """HBM bytes one fwd+bwd must move: x read and y written (forward); x, dy read and dx written
+    (backward); phi read once per pass and d_phi (fp32) written once; weight read twice, d_weight
+    written; plus the small per-token saved state (2 * (K + 2n + n^2 + 2) floats per token)."""
+    K = 2 * n + n * n
+    streams = 5 * B * n * C * io_bytes
+    phi = K * n * C * (2 * phi_bytes + 4)
+    small = C * (2 * 2 + 4) + 2 * B * (K + 2 * n + n * n + 2) * 4
+    return streams + phi + small
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index):
+        self.proc = None
+        self.path = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--id=" + uuid, "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 6 and parts[0].isdigit():
+                    rows.append(parts)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if rows:
+            clocks = sorted(int(r[0]) for r in rows)
+            # the busy half of the samples: the sampler also sees idle time around the region
+            busy = clocks[len(clocks) // 2:]
+            out["sm_mhz"] = statistics.median(busy)
+            out["sm_max_mhz"] = int(rows[0][1])
+            out["samples"] = len(rows)
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            for i, nm in enumerate(names):
+                if any(r[2 + i].lower().startswith("active") for r in rows):
+                    out["reasons"].append(nm)
+        return out
+
+
+def make_problem(cfg, device, seed):
+    from mhc.cu_b200 import synthetic
+    B, n, C, dtype = cfg["B"], cfg["n"], cfg["C"], cfg["dtype"]
+    if cfg["kind"] != "dynamic":
+        raise SystemExit("bench.py times the dynamic-H layer; pick c2, c3 or a dynamic workload")
+    params = synthetic.dynamic_params(n, C, seed=0)
+    return params, synthetic.pack_dynamic(params, dtype, device)
+
+
+def cpu_naive_tokens_per_s(cfg, min_seconds, max_runs=200):
+    """The naive PyTorch layer (the CPU oracle) on the host cores, fp32, all torch threads."""
+    import oracle
+    from mhc.cu_b200 import synthetic
+    B, n, C = cfg["B"], cfg["n"], cfg["C"]
+    params = synthetic.dynamic_params(n, C, seed=0)
+    x, dy = synthetic.streams(B, n, C, seed=0)
+    oracle.dynamic_fwd_bwd(x, params, dy, cfg["iters"], cfg["eps"], dtype=torch.float32)  # warm-up
+    t0 = time.perf_counter()
+    runs = 0
+    times = []
+    while (time.perf_counter() - t0 < min_seconds or runs < 3) and runs < max_runs:
+        t1 = time.perf_counter()
+        oracle.dynamic_fwd_bwd(x, params, dy, cfg["iters"], cfg["eps"], dtype=torch.float32)
+        times.append(time.perf_counter() - t1)
+        runs += 1
+    med = statistics.median(times)
+    return B / med, runs, med
+
+
+def run_reference(args, cfg, rank):
+    """Reference arm: the reference's own CPU path for this layer is its naive PyTorch module
+    (src/python/benchmarks/bench_layer.py:74-145 of AndreSlavescu/mHC.cu).  It is Python and does not
+    travel to the GPU box, so the pinned restatement in oracle/ is timed (kind "port")."""
+    if rank != 0:
+        return
+    import oracle
+    from mhc.cu_b200 import synthetic
+    B, n, C = cfg["B"], cfg["n"], cfg["C"]
+    params = synthetic.dynamic_params(n, C, seed=0)
+    x, dy = synthetic.streams(B, n, C, seed=0)
+    for _ in range(max(1, min(args.warmup, 3))):
+        oracle.dynamic_fwd_bwd(x, params, dy, cfg["iters"], cfg["eps"], dtype=torch.float32)
+    steps = min(args.steps, 40)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.dynamic_fwd_bwd(x, params, dy, cfg["iters"], cfg["eps"], dtype=torch.float32)
+    dt = time.perf_counter() - t0
+    val = B * steps / dt
+    cores = torch.get_num_threads()
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "n": n, "C": C, "device": "cpu",
+                   "host_cpus": os.cpu_count()},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{steps} full fwd+bwd passes over the {B}-token batch, fp32"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3")
+    ap.add_argument("--sets", type=int, default=4, help="input sets rotated to exceed L2")
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python every step")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=10.0)
+    ap.add_argument("--profile", action="store_true",
+                    help="kernel loop only (for ncu): no end-to-end leg, CPU baseline or clock sampling")
+    args = ap.parse_args()
+
+    from mhc.cu_b200 import synthetic
+    cfg = dict(synthetic.CONFIGS[args.workload])
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, cfg, rank)
+        return 0
+
+    if args.warmup < 3:
+        args.warmup = 3
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    import torch.distributed as dist
+    from mhc.cu_b200 import _lib as L
+    from mhc.cu_b200 import capi
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = L.lib()
+
+    B, n, C, dtype = cfg["B"], cfg["n"], cfg["C"], cfg["dtype"]
+    K = 2 * n + n * n
+    iters, eps = cfg["iters"], cfg["eps"]
+    tag = L.BF16 if dtype == torch.bfloat16 else L.F32
+    io_bytes = 2 if dtype == torch.bfloat16 else 4
+    params, (w, phi, alpha, bias) = make_problem(cfg, dev, 0)
+
+    # R input/output sets; every rank draws its own tokens
+    R = max(1, args.sets)
+    xs, dys, ys, dxs, saved = [], [], [], [], []
+    f32 = dict(dtype=torch.float32, device=dev)
+    for r in range(R):
+        x, dy = synthetic.streams(B, n, C, seed=1000 * rank + r)
+        xs.append(x.to(dev, dtype))
+        dys.append(dy.to(dev, dtype))
+        ys.append(torch.empty_like(xs[-1]))
+        dxs.append(torch.empty_like(xs[-1]))
+        saved.append({"rms": torch.empty(B, **f32), "rms_h": torch.empty(B, **f32),
+                      "H_pre": torch.empty(B, n, **f32), "H_post": torch.empty(B, n, **f32),
+                      "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32)})
+    # flat gradient bucket: d_phi | d_bias | d_alpha | d_rmsnorm_weight
+    nC = n * C
+    bucket = torch.zeros(K * nC + K + 3 + C + 8, **f32)
+    o = 0
+    d_phi = bucket[o:o + K * nC].view(K, nC); o += K * nC
+    d_bias = bucket[o:o + K]; o += K
+    d_alpha = bucket[o:o + 3]; o += 4        # keep the next slice 16-byte aligned
+    d_w = bucket[o:o + C]
+    ws_f = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag) + 16,
+                       dtype=torch.uint8, device=dev)
+    ws_b = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_BWD, B, n, C, iters, tag) + 16,
+                       dtype=torch.uint8, device=dev)
+
+    def launch_step(r, stream):
+        s = saved[r]
+        st = lib.mhc_dynamic_fwd(
+            ys[r].data_ptr(), s["rms"].data_ptr(), s["rms_h"].data_ptr(), s["H_pre"].data_ptr(),
+            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), xs[r].data_ptr(),
+            w.data_ptr(), phi.data_ptr(), alpha.data_ptr(), bias.data_ptr(), B, n, C, iters, eps, tag,
+            ws_f.data_ptr(), ws_f.numel(), stream)
+        L.check(st, "mhc_dynamic_fwd")
+        st = lib.mhc_dynamic_bwd(
+            dxs[r].data_ptr(), d_w.data_ptr(), d_phi.data_ptr(), d_alpha.data_ptr(), d_bias.data_ptr(),
+            dys[r].data_ptr(), xs[r].data_ptr(), w.data_ptr(), phi.data_ptr(), alpha.data_ptr(),
+            bias.data_ptr(), s["rms"].data_ptr(), s["rms_h"].data_ptr(), s["H_pre"].data_ptr(),
+            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), B, n, C, iters, eps, tag,
+            ws_b.data_ptr(), ws_b.numel(), stream)
+        L.check(st, "mhc_dynamic_bwd")
+        if world > 1:
+            dist.all_reduce(bucket)
+
+    # kernels per step (counted by the library while one step is enqueued)
+    k0 = lib.mhc_kernels_enqueued()
+    launch_step(0, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    kernels_per_step = int(lib.mhc_kernels_enqueued() - k0)
+
+    graphs = None
+    graph_note = "python launches"
+    if not args.no_graph:
+        try:
+            graphs = []
+            for r in range(R):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    launch_step(r, torch.cuda.current_stream().cuda_stream)
+                graphs.append(g)
+            graph_note = "cuda graph replay" + (" incl. all-reduce" if world > 1 else "")
+        except Exception as e:  # capture of the collective can be refused; fall back to eager
+            graphs = None
+            graph_note = f"python launches (graph capture failed: {type(e).__name__})"
+            torch.cuda.synchronize()
+
+    def step(i):
+        r = i % R
+        if graphs is not None:
+            graphs[r].replay()
+        else:
+            launch_step(r, torch.cuda.current_stream().cuda_stream)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank) if not args.profile else None
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps,
+                              "kernels_per_step": kernels_per_step, "launch": graph_note}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return 0
+    # untimed extra load: a short timed region may fall between two 50 ms clock samples
+    t_end = time.perf_counter() + 0.4
+    i = 0
+    while time.perf_counter() < t_end:
+        step(i)
+        i += 1
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = world * B * args.steps / (ms * 1e-3)
+
+    # ---- end to end through the public API, host buffers in, results out --------------------
+    import mhc
+    layer = mhc.MHCLayer(C, n, sinkhorn_iters=iters, eps=eps).to(dev)
+    with torch.no_grad():
+        for k, v in params.items():
+            getattr(layer, k).copy_(v.to(dev))
+    plist = list(layer.parameters())
+    x_h = [synthetic.streams(B, n, C, seed=1000 * rank + r)[0].to(dtype).pin_memory() for r in range(2)]
+    dy_h = [synthetic.streams(B, n, C, seed=1000 * rank + r)[1].to(dtype).pin_memory() for r in range(2)]
+    y_h = torch.empty(B, n, C, dtype=dtype).pin_memory()
+    dx_h = torch.empty(B, n, C, dtype=dtype).pin_memory()
+    n_grad = sum(p.numel() for p in plist)
+    g_h = torch.empty(n_grad, dtype=torch.float32).pin_memory()
+    x_d = torch.empty(B, n, C, dtype=dtype, device=dev)
+    dy_d = torch.empty(B, n, C, dtype=dtype, device=dev)
+
+    def e2e_step(i):
+        x_d.copy_(x_h[i % 2], non_blocking=True)
+        dy_d.copy_(dy_h[i % 2], non_blocking=True)
+        xin = x_d.detach().requires_grad_(True)
+        for p in plist:
+            p.grad = None
+        y = layer(xin)
+        y.backward(dy_d)
+        flat = torch.cat([p.grad.reshape(-1).float() for p in plist])
+        if world > 1:
+            dist.all_reduce(flat)
+        y_h.copy_(y.detach(), non_blocking=True)
+        dx_h.copy_(xin.grad, non_blocking=True)
+        g_h.copy_(flat, non_blocking=True)
+
+    e2e_steps = max(5, min(args.steps, 50))
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(e2e_steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+    e2e_value = world * B * e2e_steps / (e2e_ms * 1e-3)
+    h2d = 2 * B * n * C * io_bytes
+    d2h = 2 * B * n * C * io_bytes + n_grad * 4
+
+    if rank == 0:
+        peak, peak_kind = hbm_peak()
+        abytes = algorithmic_bytes(B, n, C, io_bytes, io_bytes)
+        achieved = abytes / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "kind": "dynamic-H fwd+bwd", "B_per_gpu": B, "n": n,
+                       "C": C, "sinkhorn_iters": iters, "eps": eps, "parallelism": f"dp{world}",
+                       "l2": f"{R} rotating input sets ({R * 4 * B * n * C * io_bytes / 1e6:.0f} MB of "
+                             f"streams) exceed the L2 cache",
+                       "launch": graph_note},
+            "gpu_launches": kernels_per_step * args.steps,
+            "kernels_per_step": kernels_per_step,
+            "clocks": {"sm_mhz": clocks["sm_mhz"], "sm_max_mhz": clocks["sm_max_mhz"],
+                       "reasons": clocks["reasons"], "samples": clocks["samples"]},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                    "api": "mhc.MHCLayer forward + backward, pinned host buffers"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_kind,
+                         "algorithmic_bytes_per_step": abytes,
+                         "scope": "all kernels of one fwd+bwd step on one GPU"},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, runs, med = cpu_naive_tokens_per_s(cfg, args.cpu_seconds)
+            line["cpu_baseline"] = {
+                "value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"{runs} full fwd+bwd passes of the naive PyTorch layer over the same "
+                          f"{B}-token batch, fp32, median {med * 1e3:.0f} ms",
+                "host_cpus": os.cpu_count()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -65,6 +65,11 @@ const char* mhc_last_cuda_error(void);
 /* ABI revision; bumped when a signature changes. */
 int mhc_abi_version(void);
 
+/* Number of kernels this library has enqueued since it was loaded (all threads and devices;
+ * launches recorded into a stream capture count once, when captured).  For benchmarks that
+ * must state how many of these kernels ran. */
+unsigned long long mhc_kernels_enqueued(void);
+
 /* Bytes of scratch a call needs for the given problem (0 is a valid answer).  For the
  * Sinkhorn ops pass B = batch, n = matrix size, C = 0.  Returns (size_t)-1 on bad arguments.
  * Replaces the grow-on-demand global MHCWorkspace (src/python/bindings.cu:166-219). */

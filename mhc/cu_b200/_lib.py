@@ -22,6 +22,7 @@ SIGNATURES = {
     "mhc_status_string": (C.c_char_p, [_i]),
     "mhc_last_cuda_error": (C.c_char_p, []),
     "mhc_abi_version": (_i, []),
+    "mhc_kernels_enqueued": (C.c_ulonglong, []),
     "mhc_workspace_bytes": (_z, [_i, _l, _i, _l, _i, _i]),
     "mhc_dynamic_fwd": (_i, [_p] * 12 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_dynamic_bwd": (_i, [_p] * 17 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),

@@ -4,8 +4,13 @@
 #include "../../../include/mhc_b200.h"
 
 #include <cstring>
+#include <type_traits>
 
 #include "kernels.h"
+
+namespace mhc {
+std::atomic<unsigned long long> g_kernels_enqueued{0};
+}
 
 namespace {
 
@@ -55,22 +60,40 @@ int check_dims(int64_t B, int n, int64_t C, int iters, int dtype) {
 
 size_t den_elem(int dtype) { return dtype == MHC_F32 ? sizeof(double) : sizeof(float); }
 
+// Partial projection results the forward produces for this shape / dtype (1 = no split).
+int proj_partials(Dims d, int dtype) {
+    if (dtype == MHC_BF16) {
+        const int packed = proj_mma_splits(d);
+        if (packed != 0) return packed & 0xffffff;
+    }
+    return 1;
+}
+
 struct DynFwdWs {
     float* praw;
     float* sumsq;
-    DynFwdWs(Carver& c, Dims d) {
-        praw = c.take<float>((size_t)d.B * d.K());
-        sumsq = c.take<float>((size_t)d.B);
+    int nsplit;
+    DynFwdWs(Carver& c, Dims d, int dtype) {
+        nsplit = proj_partials(d, dtype);
+        praw = c.take<float>((size_t)nsplit * d.B * d.K());
+        sumsq = c.take<float>((size_t)nsplit * d.B);
     }
 };
 
 struct DynBwdWs {
-    float *dH, *c2, *dpr, *qq, *partials, *dw_part;
+    float *dH, *c2, *dpr, *qq, *partials, *dw_part, *rec;
+    bf16 *dprb, *dprT;
     void* den;
     int nblk, ntb;
+    bool mma;
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
+        mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
         nblk = coeffs_dyn_bwd_blocks(d);
-        ntb = dx_token_blocks(d);
+        ntb = mma ? dx_mma_token_blocks(d) : dx_token_blocks(d);
+        const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
+        rec = c.take<float>(mma ? (size_t)d.B * bwd_mma_record_floats(d) : 0);
+        dprb = c.take<bf16>(mma ? (size_t)d.B * bwd_mma_kp(d) : 0);
+        dprT = c.take<bf16>(mma ? Bp * bwd_mma_kp(d) : 0);
         dH = c.take<float>((size_t)d.B * d.K());
         c2 = c.take<float>((size_t)d.B);
         dpr = c.take<float>((size_t)d.B * d.K());
@@ -116,10 +139,17 @@ int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post
                   const float* bias, Dims d, int iters, float eps, int dtype, void* workspace,
                   cudaStream_t s) {
     Carver c(workspace);
-    DynFwdWs ws(c, d);
-    MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
-    MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, 1, alpha, bias,
-                                  d, iters, eps, dtype == MHC_F32, s));
+    DynFwdWs ws(c, d, dtype);
+    if constexpr (std::is_same<T, bf16>::value) {
+        if (proj_mma_splits(d) != 0)
+            MHC_TRY(launch_proj_mma(ws.praw, ws.sumsq, (const bf16*)x, (const bf16*)phi, d, s));
+        else
+            MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
+    } else {
+        MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
+    }
+    MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, ws.nsplit, alpha,
+                                  bias, d, iters, eps, dtype == MHC_F32, s));
     MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1, d,
                                 eps, s));
     return MHC_OK;
@@ -135,11 +165,25 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
     DynBwdWs ws(c, d, iters, dtype);
     MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
                                  H_post, 1, rms, d, s));
+    MmaBwdOut mo;
+    if (ws.mma) {
+        mo.rec = ws.rec; mo.dprb = ws.dprb; mo.dprT = ws.dprT; mo.M = M; mo.rms = rms; mo.c2 = ws.c2;
+    }
     MHC_TRY(launch_coeffs_dyn_bwd(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
-                                  alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, s));
-    MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
-                             H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d, s));
-    MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+                                  alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, mo, s));
+    if constexpr (std::is_same<T, bf16>::value) {
+        if (ws.mma) {
+            MHC_TRY(launch_dx_mma((bf16*)dx, ws.dw_part, (const bf16*)x, (const bf16*)dy,
+                                  (const bf16*)w, ws.rec, ws.dprb, (const bf16*)phi, d, s));
+            MHC_TRY(launch_dphi_mma(d_phi, (const bf16*)x, ws.dprT, d, s));
+        }
+    }
+    if (!ws.mma) {
+        MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w,
+                                 H_pre, H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d,
+                                 s));
+        MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+    }
     MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials, ws.nblk,
                             d.n, s));
     return MHC_OK;
@@ -195,6 +239,10 @@ const char* mhc_last_cuda_error(void) { return g_last_cuda_error; }
 
 int mhc_abi_version(void) { return 1; }
 
+unsigned long long mhc_kernels_enqueued(void) {
+    return mhc::g_kernels_enqueued.load(std::memory_order_relaxed);
+}
+
 size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int dtype) {
     const bool sk = (op == MHC_OP_SINKHORN_FWD || op == MHC_OP_SINKHORN_BWD);
     const bool rn = (op == MHC_OP_RMSNORM_FWD || op == MHC_OP_RMSNORM_BWD);
@@ -207,7 +255,7 @@ size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int d
     const Dims d{B, n, sk ? 1 : C};
     Carver c(nullptr);
     switch (op) {
-        case MHC_OP_DYNAMIC_FWD: { DynFwdWs w(c, d); break; }
+        case MHC_OP_DYNAMIC_FWD: { DynFwdWs w(c, d, dtype); break; }
         case MHC_OP_DYNAMIC_BWD: { DynBwdWs w(c, d, iters, dtype); break; }
         case MHC_OP_STATIC_FWD: { StaticFwdWs w(c, d); break; }
         case MHC_OP_STATIC_BWD: { StaticBwdWs w(c, d, iters, dtype); break; }
@@ -224,9 +272,10 @@ int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_po
                     float eps, int dtype, void* workspace, size_t workspace_bytes,
                     mhc_stream_t stream) {
     if (int st = check_dims(B, n, C, iters, dtype)) return st;
-    if (!y || !rms || !rms_h || !H_pre || !H_post || !M || !proj || !x || !rmsnorm_weight || !phi ||
-        !alpha || !bias)
+    if (!rmsnorm_weight || !phi || !alpha || !bias) return MHC_ERR_NULL_POINTER;
+    if (B > 0 && (!y || !rms || !rms_h || !H_pre || !H_post || !M || !proj || !x))
         return MHC_ERR_NULL_POINTER;
+    if (B == 0) return MHC_OK;  // nothing to compute, nothing to write
     if (!aligned16(y) || !aligned16(x) || !aligned16(phi) || !aligned16(rmsnorm_weight) ||
         !aligned16(workspace))
         return MHC_ERR_MISALIGNED;
@@ -248,8 +297,11 @@ int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_al
                     int64_t B, int n, int64_t C, int iters, float eps, int dtype, void* workspace,
                     size_t workspace_bytes, mhc_stream_t stream) {
     if (int st = check_dims(B, n, C, iters, dtype)) return st;
-    if (!dx || !d_rmsnorm_weight || !d_phi || !d_alpha || !d_bias || !dy || !x || !rmsnorm_weight ||
-        !phi || !alpha || !bias || !rms || !rms_h || !H_pre || !H_post || !M || !proj)
+    if (!d_rmsnorm_weight || !d_phi || !d_alpha || !d_bias || !rmsnorm_weight || !phi || !alpha ||
+        !bias)
+        return MHC_ERR_NULL_POINTER;
+    // an empty batch has no per-token storage; the parameter gradients are still written (zeros)
+    if (B > 0 && (!dx || !dy || !x || !rms || !rms_h || !H_pre || !H_post || !M || !proj))
         return MHC_ERR_NULL_POINTER;
     if (!aligned16(dx) || !aligned16(dy) || !aligned16(x) || !aligned16(phi) || !aligned16(d_phi) ||
         !aligned16(rmsnorm_weight) || !aligned16(workspace))
@@ -273,7 +325,8 @@ int mhc_static_fwd(void* y, float* rms, float* H_pre_act, float* H_post_act, flo
                    float eps, int dtype, void* workspace, size_t workspace_bytes,
                    mhc_stream_t stream) {
     if (int st = check_dims(B, n, C, iters, dtype)) return st;
-    if (!y || !x || !rmsnorm_weight || !H_pre || !H_post || !H_res) return MHC_ERR_NULL_POINTER;
+    if (!rmsnorm_weight || !H_pre || !H_post || !H_res) return MHC_ERR_NULL_POINTER;
+    if (B > 0 && (!y || !x)) return MHC_ERR_NULL_POINTER;
     if (!aligned16(y) || !aligned16(x) || !aligned16(rmsnorm_weight) || !aligned16(workspace))
         return MHC_ERR_MISALIGNED;
     const bool need_ws = (!rms || !H_pre_act || !H_post_act || !M);
@@ -303,9 +356,10 @@ int mhc_static_bwd(void* dx, float* d_rmsnorm_weight, float* d_H_pre, float* d_H
                    float eps, int dtype, void* workspace, size_t workspace_bytes,
                    mhc_stream_t stream) {
     if (int st = check_dims(B, n, C, iters, dtype)) return st;
-    if (!dx || !d_rmsnorm_weight || !d_H_pre || !d_H_post || !d_H_res || !dy || !x ||
-        !rmsnorm_weight || !H_res || !rms || !H_pre_act || !H_post_act || !M)
+    if (!d_rmsnorm_weight || !d_H_pre || !d_H_post || !d_H_res || !rmsnorm_weight || !H_res ||
+        !H_pre_act || !H_post_act || !M)
         return MHC_ERR_NULL_POINTER;
+    if (B > 0 && (!dx || !dy || !x || !rms)) return MHC_ERR_NULL_POINTER;
     if (!aligned16(dx) || !aligned16(dy) || !aligned16(x) || !aligned16(rmsnorm_weight) ||
         !aligned16(workspace))
         return MHC_ERR_MISALIGNED;

@@ -97,7 +97,7 @@ coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __
                       const float* __restrict__ H_post, const float* __restrict__ proj,
                       const float* __restrict__ rms_h, const float* __restrict__ alpha,
                       const float* __restrict__ bias, A* __restrict__ den_ws, int64_t B, int n,
-                      int64_t nC, int iters, float eps) {
+                      int64_t nC, int iters, float eps, MmaBwdOut mo) {
     extern __shared__ float sm[];  // [GPB][K+3]
     constexpr int GPB = kCoeffThreads / G;
     const int grp = threadIdx.x / G;
@@ -107,6 +107,8 @@ coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __
     const int row = act ? lane_row : G;
     const int K = 2 * n + n * n;
     const int KP = K + 3;
+    const int K8P = (K + 7) / 8 * 8;              // row length of the bf16 copies of dpr
+    const int64_t Bp = (B + 15) / 16 * 16;        // tokens incl. padding in dprT
 
     for (int i = threadIdx.x; i < GPB * KP; i += kCoeffThreads) sm[i] = 0.f;
     __syncthreads();
@@ -146,6 +148,22 @@ coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __
         float* smg = sm + grp * KP;
         dpo[row] = (float)vp;
         dpo[n + row] = (float)vq;
+        if (mo.rec != nullptr) {
+            const int RS = (n * n + 2 * n + 3 + 3) / 4 * 4;
+            float* rc = mo.rec + tok * RS;
+            const float* Mrow = mo.M + tok * n * n + row * n;
+            for (int j = 0; j < n; ++j) rc[j * n + row] = Mrow[j];   // MT[j][row] = M[row][j]
+            rc[n * n + row] = (float)hp;
+            rc[n * n + n + row] = (float)hq;
+            if (row == 0) {
+                rc[n * n + 2 * n] = 1.f / mo.rms[tok];
+                rc[n * n + 2 * n + 1] = mo.c2[tok];
+            }
+            mo.dprb[tok * K8P + row] = __float2bfloat16_rn((float)vp);
+            mo.dprb[tok * K8P + n + row] = __float2bfloat16_rn((float)vq);
+            mo.dprT[(int64_t)row * Bp + tok] = __float2bfloat16_rn((float)vp);
+            mo.dprT[(int64_t)(n + row) * Bp + tok] = __float2bfloat16_rn((float)vq);
+        }
         smg[row] = (float)dtp;
         smg[n + row] = (float)dtq;
         qacc = vp * pp + vq * pq;
@@ -160,6 +178,10 @@ coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __
                 const A v = a2 * dtr * rinv;
                 dpo[k] = (float)v;
                 smg[k] = (float)dtr;
+                if (mo.rec != nullptr) {
+                    mo.dprb[tok * K8P + k] = __float2bfloat16_rn((float)v);
+                    mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn((float)v);
+                }
                 qacc += v * pv;
                 dal2 += dtr * pv;
             }
@@ -169,8 +191,26 @@ coeffs_dyn_bwd_kernel(float* __restrict__ dpr, float* __restrict__ qq, float* __
     dal0 = group_sum<G, A>(dal0);
     dal1 = group_sum<G, A>(dal1);
     dal2 = group_sum<G, A>(dal2);
+    if (mo.rec != nullptr && lane_row < n && tok < Bp) {
+        // zero padding: rows K..K8P-1 of every token, and every row of the tokens B..Bp-1
+        if (lane_row == 0)
+            for (int k = K; k < K8P; ++k) {
+                if (tok < B) mo.dprb[tok * K8P + k] = __float2bfloat16_rn(0.f);
+                mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn(0.f);
+            }
+        if (tok >= B) {
+            mo.dprT[(int64_t)lane_row * Bp + tok] = __float2bfloat16_rn(0.f);
+            mo.dprT[(int64_t)(n + lane_row) * Bp + tok] = __float2bfloat16_rn(0.f);
+            for (int j = 0; j < n; ++j)
+                mo.dprT[(int64_t)(2 * n + lane_row * n + j) * Bp + tok] = __float2bfloat16_rn(0.f);
+        }
+    }
     if (act && lane_row == 0) {
         qq[tok] = (float)(qacc / (A(nC) * r));
+        if (mo.rec != nullptr) {
+            const int RS = (n * n + 2 * n + 3 + 3) / 4 * 4;
+            mo.rec[tok * RS + n * n + 2 * n + 2] = (float)(qacc / (A(nC) * r));
+        }
         float* smg = sm + grp * KP;
         smg[K] = (float)dal0;
         smg[K + 1] = (float)dal1;
@@ -366,30 +406,35 @@ cudaError_t launch_coeffs_dyn_fwd(float* H_pre, float* H_post, float* M, float* 
             coeffs_dyn_fwd_kernel<G, float><<<grid, kCoeffThreads, 0, s>>>(
                 H_pre, H_post, M, proj, rms_h, praw, sumsq, nsplit, alpha, bias, d.B, d.n, d.nC(),
                 iters, eps);
-        return cudaPeekAtLastError();
+        return launched();
     });
 }
 
-int coeffs_dyn_bwd_blocks(Dims d) { return (int)blocks_for(d.B, group_lanes(d.n) < 2 ? 2 : group_lanes(d.n)); }
+int coeffs_dyn_bwd_blocks(Dims d) {
+    // sized for the padded token count the tensor-core backward asks for
+    return (int)blocks_for((d.B + 15) / 16 * 16, group_lanes(d.n) < 2 ? 2 : group_lanes(d.n));
+}
 
 cudaError_t launch_coeffs_dyn_bwd(float* dpr, float* qq, float* partials, const float* dH,
                                   const float* H_pre, const float* H_post, const float* proj,
                                   const float* rms_h, const float* alpha, const float* bias,
                                   void* den_ws, Dims d, int iters, float eps, bool use_double,
-                                  cudaStream_t s) {
+                                  MmaBwdOut mo, cudaStream_t s) {
     if (d.B == 0) return cudaSuccess;
     return dispatch_group(d.n, [&]<int G>() -> cudaError_t {
-        const unsigned grid = blocks_for(d.B, G);
+        // the padding tokens up to a multiple of 16 get a group too (they write the zero padding
+        // of the bf16 copies and all-zero partial rows), matching coeffs_dyn_bwd_blocks()
+        const unsigned grid = blocks_for((d.B + 15) / 16 * 16, G);
         const size_t smem = (size_t)(kCoeffThreads / G) * (d.K() + 3) * sizeof(float);
         if (use_double)
             coeffs_dyn_bwd_kernel<G, double><<<grid, kCoeffThreads, smem, s>>>(
                 dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (double*)den_ws, d.B,
-                d.n, d.nC(), iters, eps);
+                d.n, d.nC(), iters, eps, mo);
         else
             coeffs_dyn_bwd_kernel<G, float><<<grid, kCoeffThreads, smem, s>>>(
                 dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (float*)den_ws, d.B,
-                d.n, d.nC(), iters, eps);
-        return cudaPeekAtLastError();
+                d.n, d.nC(), iters, eps, mo);
+        return launched();
     });
 }
 
@@ -403,7 +448,7 @@ cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float*
         else
             coeffs_static_fwd_kernel<G, float><<<1, 32, 0, s>>>(H_pre_act, H_post_act, M, H_pre,
                                                                 H_post, H_res, n, iters, eps);
-        return cudaPeekAtLastError();
+        return launched();
     });
 }
 
@@ -425,7 +470,7 @@ cudaError_t launch_coeffs_static_bwd(float* d_H_pre, float* d_H_post, float* d_H
             coeffs_static_bwd_kernel<G, float><<<1, 1024, smem, s>>>(
                 d_H_pre, d_H_post, d_H_res, dH, H_pre_act, H_post_act, H_res, (float*)den_ws, d.B,
                 d.n, iters, eps, P, TL);
-        return cudaPeekAtLastError();
+        return launched();
     });
 }
 
@@ -435,7 +480,7 @@ cudaError_t launch_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int
     return dispatch_group(n, [&]<int G>() -> cudaError_t {
         sinkhorn_fwd_kernel<G, float><<<blocks_for(batch, G), kCoeffThreads, 0, s>>>(
             out, inp, batch, n, iters, eps);
-        return cudaPeekAtLastError();
+        return launched();
     });
 }
 
@@ -446,7 +491,7 @@ cudaError_t launch_sinkhorn_bwd(float* d_inp, const float* grad, const float* in
     return dispatch_group(n, [&]<int G>() -> cudaError_t {
         sinkhorn_bwd_kernel<G, double><<<blocks_for(batch, G), kCoeffThreads, 0, s>>>(
             d_inp, grad, inp, (double*)den_ws, batch, n, iters, eps);
-        return cudaPeekAtLastError();
+        return launched();
     });
 }
 

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace mhc {
@@ -18,6 +20,14 @@ struct Dims {
     int K() const { return 2 * n + n * n; }
     int64_t nC() const { return (int64_t)n * C; }
 };
+
+// Number of kernels enqueued by this library since it was loaded (all threads, all devices).
+// Every launcher calls launched() once per kernel it enqueues.
+extern std::atomic<unsigned long long> g_kernels_enqueued;
+inline cudaError_t launched(int kernels = 1) {
+    g_kernels_enqueued.fetch_add((unsigned long long)kernels, std::memory_order_relaxed);
+    return cudaPeekAtLastError();
+}
 
 // Smallest power of two >= n (n in 1..32): lanes per Sinkhorn group.
 inline int group_lanes(int n) {
@@ -35,11 +45,22 @@ cudaError_t launch_coeffs_dyn_fwd(float* H_pre, float* H_post, float* M, float* 
 // den_ws: B * G * 2 * iters elements of float / double.  partials: [blocks][K+3]; returns the
 // number of blocks through *nblocks (callable with all pointers NULL to query it).
 int coeffs_dyn_bwd_blocks(Dims d);
+// Optional outputs for the tensor-core backward (all NULL to skip): rec [B][record floats],
+// dprb bf16 [B][KP], dprT bf16 [KP][Bp] with Bp = B rounded up to 16 (padding written as zero);
+// they need rms [B] and c2 [B] as extra inputs.
+struct MmaBwdOut {
+    float* rec = nullptr;
+    bf16* dprb = nullptr;
+    bf16* dprT = nullptr;
+    const float* M = nullptr;
+    const float* rms = nullptr;
+    const float* c2 = nullptr;
+};
 cudaError_t launch_coeffs_dyn_bwd(float* dpr, float* qq, float* partials, const float* dH,
                                   const float* H_pre, const float* H_post, const float* proj,
                                   const float* rms_h, const float* alpha, const float* bias,
                                   void* den_ws, Dims d, int iters, float eps, bool use_double,
-                                  cudaStream_t s);
+                                  MmaBwdOut mma, cudaStream_t s);
 cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float* M,
                                      const float* H_pre, const float* H_post, const float* H_res,
                                      int n, int iters, float eps, bool use_double, cudaStream_t s);
@@ -78,6 +99,23 @@ cudaError_t launch_proj(float* praw, float* sumsq, const T* x, const T* phi, Dim
                         cudaStream_t s);
 template <typename T>
 cudaError_t launch_dphi(float* dphi, const T* x, const float* dpr, Dims d, cudaStream_t s);
+
+// ---- proj_mma.cu: the bf16 projection on the tensor cores --------------------------------------
+// proj_mma_splits: 0 if the shape is not covered, else (partials | chunks << 24); the partial
+// results praw_part[partials][B][K], sumsq_part[partials][B] are summed by the coefficient kernel.
+int proj_mma_splits(Dims d);
+cudaError_t launch_proj_mma(float* praw_part, float* sumsq_part, const bf16* x, const bf16* phi,
+                            Dims d, cudaStream_t s);
+
+// ---- bwd_mma.cu: bf16 backward passes with tensor-core contractions against phi ---------------
+bool bwd_mma_supported(Dims d);
+int bwd_mma_kp(Dims d);              // K rounded up to 8
+int bwd_mma_record_floats(Dims d);   // floats per token record
+int dx_mma_token_blocks(Dims d);     // rows of dw_part the dx pass writes
+cudaError_t launch_dx_mma(bf16* dx, float* dw_part, const bf16* x, const bf16* g, const bf16* w,
+                          const float* rec, const bf16* dprb, const bf16* phi, Dims d,
+                          cudaStream_t s);
+cudaError_t launch_dphi_mma(float* dphi, const bf16* x, const bf16* dprT, Dims d, cudaStream_t s);
 
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,

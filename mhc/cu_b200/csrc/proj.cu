@@ -151,7 +151,7 @@ cudaError_t launch_proj(float* praw, float* sumsq, const T* x, const T* phi, Dim
         proj_kernel<T, VW><<<grid, kProjThreads, 0, s>>>(praw, sumsq, x, phi, d.B, K, d.nC());
     else
         proj_kernel<T, 1><<<grid, kProjThreads, 0, s>>>(praw, sumsq, x, phi, d.B, K, d.nC());
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 template <typename T>
@@ -166,7 +166,7 @@ cudaError_t launch_dphi(float* dphi, const T* x, const float* dpr, Dims d, cudaS
         dphi_kernel<T, VW><<<grid, block, 0, s>>>(dphi, x, dpr, d.B, K, d.nC());
     else
         dphi_kernel<T, 1><<<grid, block, 0, s>>>(dphi, x, dpr, d.B, K, d.nC());
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 template cudaError_t launch_proj<float>(float*, float*, const float*, const float*, Dims,

@@ -137,7 +137,7 @@ cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf1
         rmsnorm_fwd_kernel<8><<<(unsigned)B, row_threads(C / 8), 0, s>>>(out, rms, inp, w, C, eps);
     else
         rmsnorm_fwd_kernel<1><<<(unsigned)B, row_threads(C), 0, s>>>(out, rms, inp, w, C, eps);
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 int rmsnorm_bwd_blocks(int64_t B) { return (int)((B + kRmsRowsPerBlock - 1) / kRmsRowsPerBlock); }
@@ -159,7 +159,7 @@ cudaError_t launch_rmsnorm_bwd(bf16* d_inp, float* d_w, float* dw_part, const bf
             const dim3 grid((unsigned)((C + 31) / 32), (unsigned)nparts);
             rmsnorm_bwd_dw_kernel<1><<<grid, block, 0, s>>>(dw_part, grad, inp, rms, B, C);
         }
-        cudaError_t e = cudaPeekAtLastError();
+        cudaError_t e = launched(2);
         if (e != cudaSuccess) return e;
     }
     return launch_finalize(d_w, dw_part, nparts, C, nullptr, nullptr, nullptr, 0, 1, s);

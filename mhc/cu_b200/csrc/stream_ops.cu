@@ -392,7 +392,7 @@ static cudaError_t apply_fwd_pick(T* y, float* rho, const T* x, const bf16* w, c
         MHC_APPLY(0, MAXT);
     }
 #undef MHC_APPLY
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 template <typename T>
@@ -432,7 +432,7 @@ cudaError_t launch_bwd_reduce(float* dH, float* c2, const T* x, const T* g, cons
         if (vec) MHC_RED(VW, 8); else MHC_RED(1, 8);
     }
 #undef MHC_RED
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 int dx_token_blocks(Dims d) { return (int)((d.B + kDxTokens - 1) / kDxTokens); }
@@ -465,7 +465,7 @@ cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const b
     }
 #undef MHC_DX2
 #undef MHC_DX
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
@@ -476,7 +476,7 @@ cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_
     const unsigned grid = (unsigned)((items + 255) / 256);
     finalize_kernel<<<grid, 256, 0, s>>>(d_w, dw_part, nparts, C, d_bias, d_alpha, partials, nparts2,
                                          K);
-    return cudaPeekAtLastError();
+    return launched();
 }
 
 #define MHC_INSTANTIATE(T)                                                                         \

@@ -105,6 +105,10 @@ def dynamic_backward_closed_form(x, params, dy, iters=20, eps=1e-5, dtype=torch.
     db = dt.sum(dim=0)
     dtp = dt * p
     dalpha = torch.stack([dtp[:, :n].sum(), dtp[:, n:2 * n].sum(), dtp[:, 2 * n:].sum()])
+    # sum of |terms| behind each alpha gradient: the scale against which its rounding error is
+    # meaningful (the signed sum itself can cancel to almost nothing)
+    dalpha_scale = torch.stack([dtp[:, :n].abs().sum(), dtp[:, n:2 * n].abs().sum(),
+                                dtp[:, 2 * n:].abs().sum()])
     dpr = dt * alpha / r                             # dp / r
     dphi = dpr.t() @ x_flat
     qq = (dpr * p).sum(dim=-1, keepdim=True) / (nC * r)
@@ -115,6 +119,8 @@ def dynamic_backward_closed_form(x, params, dy, iters=20, eps=1e-5, dtype=torch.
         "dphi_pre": dphi[:n], "dphi_post": dphi[n:2 * n], "dphi_res": dphi[2 * n:],
         "dalpha_pre": dalpha[0], "dalpha_post": dalpha[1], "dalpha_res": dalpha[2],
         "db_pre": db[:n], "db_post": db[n:2 * n], "db_res": db[2 * n:].view(n, n),
+        "scale_dalpha_pre": dalpha_scale[0], "scale_dalpha_post": dalpha_scale[1],
+        "scale_dalpha_res": dalpha_scale[2],
     }
 
 
