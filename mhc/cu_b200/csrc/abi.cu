@@ -148,6 +148,12 @@ int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post
     } else {
         MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
     }
+    if (mix_fwd_supported(d, sizeof(T))) {
+        MHC_TRY(launch_mix_fwd_dynamic<T>((T*)y, rms, rms_h, H_pre, H_post, M, proj, (const T*)x,
+                                          (const bf16*)w, ws.praw, ws.sumsq, ws.nsplit, alpha, bias,
+                                          nullptr, d, iters, eps, dtype == MHC_F32, s));
+        return MHC_OK;
+    }
     MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, ws.nsplit, alpha,
                                   bias, d, iters, eps, dtype == MHC_F32, s));
     MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1, d,
@@ -195,6 +201,11 @@ int static_fwd_t(void* y, float* rms, float* hp, float* hq, float* M, const void
                  float eps, int dtype, cudaStream_t s) {
     MHC_TRY(launch_coeffs_static_fwd(hp, hq, M, H_pre, H_post, H_res, d.n, iters, eps,
                                      dtype == MHC_F32, s));
+    if (mix_fwd_supported(d, sizeof(T))) {
+        MHC_TRY(launch_mix_fwd_static<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, nullptr,
+                                         d, eps, s));
+        return MHC_OK;
+    }
     MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, 0, d, eps, s));
     return MHC_OK;
 }

@@ -1,0 +1,72 @@
+// Asynchronous bulk copies (TMA, cp.async.bulk) from global to shared memory, completed on an
+// mbarrier.  Every wait is bounded: a wait that does not finish within kWaitCycles reports failure
+// instead of spinning forever, the kernel then records an error code in its status word and
+// returns without touching the data.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mhc {
+
+// error codes a kernel may OR into its device status word
+constexpr int kDevErrBulkWait = 1;   // a bulk-copy wait ran out
+
+constexpr long long kWaitCycles = 2000000000LL;   // about one second of SM clocks
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(arrivals)
+                 : "memory");
+}
+
+// makes the initialised barrier visible to the async proxy that will complete it
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// one arrival plus the announcement of `bytes` that an async copy will deliver
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Waits for the phase with the given parity; false if it did not complete in kWaitCycles.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > kWaitCycles) return false;
+    }
+    return true;
+}
+
+// global -> shared bulk copy of `bytes` (a multiple of 16; both addresses 16-byte aligned),
+// completing `bytes` of transaction count on `bar`.  No multicast.
+__device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes,
+                                              uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar))
+        : "memory");
+}
+
+}  // namespace mhc

@@ -117,6 +117,19 @@ cudaError_t launch_dx_mma(bf16* dx, float* dw_part, const bf16* x, const bf16* g
                           cudaStream_t s);
 cudaError_t launch_dphi_mma(float* dphi, const bf16* x, const bf16* dprT, Dims d, cudaStream_t s);
 
+// ---- mix_fwd.cu: fused forward (coefficients + aggregate + RMSNorm + distribute/mix) -----------
+bool mix_fwd_supported(Dims d, size_t elem_bytes);
+template <typename T>
+cudaError_t launch_mix_fwd_dynamic(T* y, float* rho, float* rms_h, float* H_pre, float* H_post,
+                                   float* M, float* proj, const T* x, const bf16* w,
+                                   const float* praw, const float* sumsq, int nsplit,
+                                   const float* alpha, const float* bias, int* status, Dims d,
+                                   int iters, float eps, bool use_double, cudaStream_t s);
+template <typename T>
+cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                                  const float* H_post, const float* M, int* status, Dims d,
+                                  float eps, cudaStream_t s);
+
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,
                                int64_t C, float eps, cudaStream_t s);

@@ -1,0 +1,342 @@
+// Forward pass over the streams, one small block per token:
+//
+//   * thread 0 starts ONE bulk async copy (TMA, cp.async.bulk) of the token's whole [n, C] row
+//     block into shared memory; nothing else waits on registers, so ten such blocks fit on an SM
+//     and about 200 KB per SM are in flight, which is what saturates HBM at these sizes;
+//   * while the copy is in flight the block turns the token's projection partial sums into its
+//     coefficients (RMS scale, sigmoid / 2*sigmoid / exp, Sinkhorn-Knopp held in the registers of
+//     one thread) — dynamic-H only; the static layer reads the shared coefficients instead;
+//   * pass 1 over shared memory: a = sum_i H_pre[i] x[i,:] and its sum of squares -> rho;
+//   * pass 2 over shared memory: y[i,:] = sum_j M[i,j] x[j,:] + H_post[i] * a / rho * w.
+//
+// x is read from HBM once and y written once; the coefficient kernel launch of the three-kernel
+// forward disappears.
+//
+// Takes over fused_h_activations, sinkhorn_knopp_forward_batched, stream_aggregate_bf16_dynamic,
+// rmsnorm_forward_with_rms and stream_distribute_mix_add_fused_dynamic of the reference
+// (src/csrc/include/utils.cuh:49-126, src/csrc/kernels/sinkhorn_knopp.cuh:827-1046,
+// src/csrc/kernels/stream_ops.cuh:451-642, src/csrc/kernels/rmsnorm.cuh:13-232).
+#include "async.cuh"
+#include "kernels.h"
+#include "sinkhorn.cuh"
+
+namespace mhc {
+
+namespace {
+
+constexpr int kMixThreads = 64;
+
+template <typename A>
+__device__ __forceinline__ A mix_sqrt(A v);
+template <>
+__device__ __forceinline__ float mix_sqrt<float>(float v) { return sqrtf(v); }
+template <>
+__device__ __forceinline__ double mix_sqrt<double>(double v) { return sqrt(v); }
+
+template <typename T>
+struct MixFwdParams {
+    T* y;
+    float* rho;          // [B] out
+    const T* x;
+    const bf16* w;
+    // coefficients: outputs for the dynamic layer (per token), inputs for the static one (shared)
+    float* H_pre;
+    float* H_post;
+    float* M;
+    // dynamic only
+    float* proj;         // [B][K] out, normalised projections
+    float* rms_h;        // [B] out
+    const float* praw;   // [nsplit][B][K]
+    const float* sumsq;  // [nsplit][B]
+    const float* alpha;  // [3]
+    const float* bias;   // [K]
+    int nsplit;
+    int iters;
+    int* status;         // device status word (may be NULL)
+    int64_t B;
+    int64_t C;
+    int n;
+    float eps;
+};
+
+// shared memory: [row block: n*C elements of T][coef floats][barrier]
+template <typename T, int V, int MAXN, bool DYN, typename A>
+__global__ void __launch_bounds__(kMixThreads)
+mix_fwd_kernel(const MixFwdParams<T> p) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const int n = p.n;
+    const int64_t C = p.C;
+    const int64_t b = blockIdx.x;
+    const int K = 2 * n + n * n;
+    const uint32_t row_bytes = (uint32_t)(n * C * sizeof(T));
+    T* xs = reinterpret_cast<T*>(smem_raw);
+    float* cf = reinterpret_cast<float*>(smem_raw + ((row_bytes + 127) & ~127u));
+    // cf layout: [0,K] partial sums (K projections + sum of squares) then, from cfc on:
+    // hp[MAXN] hq[MAXN] m[MAXN*MAXN] | red[2] | flags
+    float* cfc = cf + ((K + 1 + 3) & ~3);
+    float* red = cfc + 2 * MAXN + MAXN * MAXN;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(red + 4);
+    const int tid = threadIdx.x;
+#ifdef MHC_PHASE_CLOCKS
+    long long stamp[8];
+    int nstamp = 0;
+#define MHC_STAMP() stamp[nstamp++] = clock64()
+#else
+#define MHC_STAMP()
+#endif
+    MHC_STAMP();
+
+    if (tid == 0) {
+        mbar_init(bar, 1);
+        mbar_init_fence();
+        mbar_arrive_expect_tx(bar, row_bytes);
+        bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
+    }
+
+    if constexpr (DYN) {
+        // 1a. sum the split partial results of this token
+        for (int k = tid; k <= K; k += kMixThreads) {
+            const float* src = (k < K) ? p.praw + b * K + k : p.sumsq + b;
+            const int64_t st = (k < K) ? p.B * K : p.B;
+            float v = 0.f;
+            int s = 0;
+            for (; s + 4 <= p.nsplit; s += 4) {   // four loads in flight per round trip
+                const float a0 = src[(s + 0) * st], a1 = src[(s + 1) * st];
+                const float a2 = src[(s + 2) * st], a3 = src[(s + 3) * st];
+                v += (a0 + a1) + (a2 + a3);
+            }
+            for (; s < p.nsplit; ++s) v += src[s * st];
+            cf[k] = v;
+        }
+        __syncthreads();
+        MHC_STAMP();
+        // 1b. activations, one output per thread
+        const A r = mix_sqrt<A>(A(cf[K]) / A(n * C) + A(p.eps));
+        const A rinv = A(1) / r;
+        for (int k = tid; k < K; k += kMixThreads) {
+            const A pv = A(cf[k]) * rinv;
+            p.proj[b * K + k] = (float)pv;
+            if (k < n) {
+                const float h = (float)sk_sigmoid<A>(A(p.alpha[0]) * pv + A(p.bias[k]));
+                cfc[k] = h;
+                p.H_pre[b * n + k] = h;
+            } else if (k < 2 * n) {
+                const float h = (float)(A(2) * sk_sigmoid<A>(A(p.alpha[1]) * pv + A(p.bias[k])));
+                cfc[MAXN + (k - n)] = h;
+                p.H_post[b * n + (k - n)] = h;
+            } else {
+                // E kept in fp32 shared memory; the Sinkhorn thread widens it again
+                const int e = k - 2 * n;
+                cfc[2 * MAXN + (e / n) * MAXN + (e % n)] =
+                    (float)sk_exp<A>(A(p.alpha[2]) * pv + A(p.bias[k]));
+            }
+        }
+        if (tid == 0) p.rms_h[b] = (float)r;
+        __syncthreads();
+        MHC_STAMP();
+        // 1c. Sinkhorn-Knopp in the registers of one thread
+        if (tid == 0) {
+            A m[MAXN][MAXN];
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    m[i][j] = (i < n && j < n) ? A(cfc[2 * MAXN + i * MAXN + j]) : A(0);
+            sk_forward_thread<MAXN, A, false>(m, n, p.iters, A(p.eps), nullptr);
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    if (i < n && j < n) {
+                        cfc[2 * MAXN + i * MAXN + j] = (float)m[i][j];
+                        p.M[b * n * n + i * n + j] = (float)m[i][j];
+                    }
+        }
+        __syncthreads();
+    } else {
+        for (int k = tid; k < n; k += kMixThreads) {
+            cfc[k] = p.H_pre[k];
+            cfc[MAXN + k] = p.H_post[k];
+        }
+        for (int k = tid; k < n * n; k += kMixThreads)
+            cfc[2 * MAXN + (k / n) * MAXN + (k % n)] = p.M[k];
+        __syncthreads();
+    }
+
+    MHC_STAMP();
+    float hp[MAXN], hq[MAXN], m[MAXN][MAXN];
+#pragma unroll
+    for (int i = 0; i < MAXN; ++i) {
+        hp[i] = (i < n) ? cfc[i] : 0.f;
+        hq[i] = (i < n) ? cfc[MAXN + i] : 0.f;
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) m[i][j] = (i < n && j < n) ? cfc[2 * MAXN + i * MAXN + j] : 0.f;
+    }
+
+    // 2. the row block has to have landed; the vote keeps the decision uniform over the block
+    const int ok = __syncthreads_and(mbar_wait_bounded(bar, 0) ? 1 : 0);
+    if (!ok) {
+        if (tid == 0 && p.status != nullptr) atomicOr(p.status, kDevErrBulkWait);
+        return;
+    }
+
+    MHC_STAMP();
+    const int64_t nvec = C / V;
+    // 3. pass 1: sum of squares of the aggregated stream
+    float ss = 0.f;
+#pragma unroll 2
+    for (int64_t v = tid; v < nvec; v += kMixThreads) {
+        float a[V];
+#pragma unroll
+        for (int e = 0; e < V; ++e) a[e] = 0.f;
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                float xv[V];
+                load_vec<V>(xs + i * C + v * V, xv);
+#pragma unroll
+                for (int e = 0; e < V; ++e) a[e] = fmaf(hp[i], xv[e], a[e]);
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < V; ++e) ss = fmaf(a[e], a[e], ss);
+    }
+    ss = warp_sum(ss);
+    if ((tid & 31) == 0) red[tid >> 5] = ss;
+    __syncthreads();
+    const float tot = red[0] + red[1];
+    const float rho = sqrtf(tot / (float)C + p.eps);
+    const float ri = 1.f / rho;
+    if (tid == 0) p.rho[b] = rho;
+    MHC_STAMP();
+
+    // 4. pass 2: outputs
+    T* yb = p.y + b * n * C;
+#pragma unroll 2
+    for (int64_t v = tid; v < nvec; v += kMixThreads) {
+        float xv[MAXN][V], yn[V], wv[V];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                load_vec<V>(xs + i * C + v * V, xv[i]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < V; ++e) xv[i][e] = 0.f;
+            }
+        }
+        load_weight<V>(p.w, v * V, wv);
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+            float a = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) a = fmaf(hp[i], xv[i][e], a);
+            yn[e] = a * ri * wv[e];
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                float o[V];
+#pragma unroll
+                for (int e = 0; e < V; ++e) {
+                    float t = hq[i] * yn[e];
+#pragma unroll
+                    for (int j = 0; j < MAXN; ++j) t = fmaf(m[i][j], xv[j][e], t);
+                    o[e] = t;
+                }
+                store_vec<V>(yb + i * C + v * V, o);
+            }
+        }
+    }
+#ifdef MHC_PHASE_CLOCKS
+    MHC_STAMP();
+    // debug build only: block 7 overwrites the start of rms_h with its phase clocks
+    __syncthreads();
+    if (b == 7 && tid == 0 && p.rms_h != nullptr)
+        for (int i = 0; i < nstamp; ++i) reinterpret_cast<long long*>(p.rms_h)[16 + i] = stamp[i] - stamp[0];
+#endif
+#undef MHC_STAMP
+}
+
+}  // namespace
+
+// ---- host side ---------------------------------------------------------------------------------
+static size_t mix_fwd_smem(Dims d, size_t elem, int maxn) {
+    const size_t row = ((size_t)d.n * d.C * elem + 127) & ~size_t(127);
+    const size_t K = d.K();
+    return row + ((K + 1 + 3) & ~size_t(3)) * 4 + (2 * maxn + maxn * maxn + 4) * 4 + 16;
+}
+
+// The fused forward covers n <= 8, rows that are whole 16-byte vectors and fit in shared memory
+// next to a few co-resident blocks.
+bool mix_fwd_supported(Dims d, size_t elem) {
+    const int V = (int)(16 / elem);
+    if (d.n > 8 || d.C % V != 0) return false;
+    return mix_fwd_smem(d, elem, 8) <= 96 * 1024;
+}
+
+template <typename T, int MAXN, bool DYN>
+static cudaError_t mix_fwd_launch(const MixFwdParams<T>& p, Dims d, bool use_double,
+                                  cudaStream_t s) {
+    constexpr int V = VecWidth<T>::value;
+    const size_t smem = mix_fwd_smem(d, sizeof(T), MAXN);
+    const unsigned grid = (unsigned)d.B;
+    cudaError_t e;
+    if (use_double) {
+        auto k = mix_fwd_kernel<T, V, MAXN, DYN, double>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e != cudaSuccess) return e;
+        k<<<grid, kMixThreads, smem, s>>>(p);
+    } else {
+        auto k = mix_fwd_kernel<T, V, MAXN, DYN, float>;
+        e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+        if (e != cudaSuccess) return e;
+        k<<<grid, kMixThreads, smem, s>>>(p);
+    }
+    return launched();
+}
+
+template <typename T>
+cudaError_t launch_mix_fwd_dynamic(T* y, float* rho, float* rms_h, float* H_pre, float* H_post,
+                                   float* M, float* proj, const T* x, const bf16* w,
+                                   const float* praw, const float* sumsq, int nsplit,
+                                   const float* alpha, const float* bias, int* status, Dims d,
+                                   int iters, float eps, bool use_double, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (!mix_fwd_supported(d, sizeof(T))) return cudaErrorNotSupported;
+    MixFwdParams<T> p{};
+    p.y = y; p.rho = rho; p.x = x; p.w = w; p.H_pre = H_pre; p.H_post = H_post; p.M = M;
+    p.proj = proj; p.rms_h = rms_h; p.praw = praw; p.sumsq = sumsq; p.alpha = alpha; p.bias = bias;
+    p.nsplit = nsplit; p.iters = iters; p.status = status; p.B = d.B; p.C = d.C; p.n = d.n;
+    p.eps = eps;
+    return d.n <= 4 ? mix_fwd_launch<T, 4, true>(p, d, use_double, s)
+                    : mix_fwd_launch<T, 8, true>(p, d, use_double, s);
+}
+
+template <typename T>
+cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                                  const float* H_post, const float* M, int* status, Dims d,
+                                  float eps, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (!mix_fwd_supported(d, sizeof(T))) return cudaErrorNotSupported;
+    MixFwdParams<T> p{};
+    p.y = y; p.rho = rho; p.x = x; p.w = w;
+    p.H_pre = const_cast<float*>(H_pre); p.H_post = const_cast<float*>(H_post);
+    p.M = const_cast<float*>(M);
+    p.status = status; p.B = d.B; p.C = d.C; p.n = d.n; p.eps = eps;
+    return d.n <= 4 ? mix_fwd_launch<T, 4, false>(p, d, false, s)
+                    : mix_fwd_launch<T, 8, false>(p, d, false, s);
+}
+
+#define MHC_INST(T)                                                                                \
+    template cudaError_t launch_mix_fwd_dynamic<T>(T*, float*, float*, float*, float*, float*,     \
+                                                   float*, const T*, const bf16*, const float*,    \
+                                                   const float*, int, const float*, const float*,  \
+                                                   int*, Dims, int, float, bool, cudaStream_t);    \
+    template cudaError_t launch_mix_fwd_static<T>(T*, float*, const T*, const bf16*, const float*, \
+                                                  const float*, const float*, int*, Dims, float,   \
+                                                  cudaStream_t);
+MHC_INST(float)
+MHC_INST(bf16)
+#undef MHC_INST
+
+}  // namespace mhc

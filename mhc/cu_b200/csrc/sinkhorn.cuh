@@ -107,4 +107,142 @@ __device__ __forceinline__ void sk_backward(A (&d)[G], A (&y)[G], int n, int row
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// One thread owns a whole n x n matrix (n <= MAXN <= 8) in registers: no shuffles, and the n rows
+// (columns) of a step are independent chains, which is what keeps the 2*iters-step dependency
+// chain short.
+template <typename A>
+__device__ __forceinline__ A sk_rcp(A v);
+template <>
+__device__ __forceinline__ float sk_rcp<float>(float v) {
+    // one MUFU instruction (about 1 ulp); every step renormalises, so the error does not build up
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(v));
+    return r;
+}
+template <>
+__device__ __forceinline__ double sk_rcp<double>(double v) { return 1.0 / v; }
+
+// den (optional): den[(2t) * MAXN + i] = row sum + eps of row i at iteration t,
+//                 den[(2t+1) * MAXN + j] = column sum + eps of column j.
+template <int MAXN, typename A, bool STORE>
+__device__ __forceinline__ void sk_forward_thread_full(A (&m)[MAXN][MAXN], int iters, A eps,
+                                                       A* den) {
+    // n == MAXN: no size guards, so the MAXN row (column) chains are straight-line code
+    for (int t = 0; t < iters; ++t) {
+        A inv[MAXN];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            A rs = m[i][0];
+#pragma unroll
+            for (int j = 1; j < MAXN; ++j) rs += m[i][j];
+            const A rd = rs + eps;
+            inv[i] = sk_rcp<A>(rd);
+            if (STORE) den[(2 * t) * MAXN + i] = rd;
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+            for (int j = 0; j < MAXN; ++j) m[i][j] *= inv[i];
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) {
+            A cs = m[0][j];
+#pragma unroll
+            for (int i = 1; i < MAXN; ++i) cs += m[i][j];
+            const A cd = cs + eps;
+            inv[j] = sk_rcp<A>(cd);
+            if (STORE) den[(2 * t + 1) * MAXN + j] = cd;
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+            for (int j = 0; j < MAXN; ++j) m[i][j] *= inv[j];
+    }
+}
+
+template <int MAXN, typename A, bool STORE>
+__device__ __forceinline__ void sk_forward_thread(A (&m)[MAXN][MAXN], int n, int iters, A eps,
+                                                  A* den) {
+    if (n == MAXN) {
+        sk_forward_thread_full<MAXN, A, STORE>(m, iters, eps, den);
+        return;
+    }
+    for (int t = 0; t < iters; ++t) {
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                A rs = A(0);
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    if (j < n) rs += m[i][j];
+                const A rd = rs + eps;
+                const A inv = sk_rcp<A>(rd);
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    if (j < n) m[i][j] *= inv;
+                if (STORE) den[(2 * t) * MAXN + i] = rd;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) {
+            if (j < n) {
+                A cs = A(0);
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i)
+                    if (i < n) cs += m[i][j];
+                const A cd = cs + eps;
+                const A inv = sk_rcp<A>(cd);
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i)
+                    if (i < n) m[i][j] *= inv;
+                if (STORE) den[(2 * t + 1) * MAXN + j] = cd;
+            }
+        }
+    }
+}
+
+// Reverse sweep; d = dL/dM on entry and dL/dE on return, y = M on entry and E (rebuilt) on return.
+template <int MAXN, typename A>
+__device__ __forceinline__ void sk_backward_thread(A (&d)[MAXN][MAXN], A (&y)[MAXN][MAXN], int n,
+                                                   int iters, const A* den) {
+    for (int t = iters - 1; t >= 0; --t) {
+#pragma unroll
+        for (int j = 0; j < MAXN; ++j) {
+            if (j < n) {
+                const A cd = den[(2 * t + 1) * MAXN + j];
+                const A inv = sk_rcp<A>(cd);
+                A tc = A(0);
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i)
+                    if (i < n) tc += d[i][j] * y[i][j];
+#pragma unroll
+                for (int i = 0; i < MAXN; ++i) {
+                    if (i < n) {
+                        d[i][j] = (d[i][j] - tc) * inv;
+                        y[i][j] *= cd;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i) {
+            if (i < n) {
+                const A rd = den[(2 * t) * MAXN + i];
+                const A inv = sk_rcp<A>(rd);
+                A tr = A(0);
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j)
+                    if (j < n) tr += d[i][j] * y[i][j];
+#pragma unroll
+                for (int j = 0; j < MAXN; ++j) {
+                    if (j < n) {
+                        d[i][j] = (d[i][j] - tr) * inv;
+                        y[i][j] *= rd;
+                    }
+                }
+            }
+        }
+    }
+}
+
 }  // namespace mhc
