@@ -153,6 +153,24 @@ int mhc_sinkhorn_bwd(float* d_inp, const float* grad_out, const float* inp, int6
                      int iters, float eps, void* workspace, size_t workspace_bytes,
                      mhc_stream_t stream);
 
+/* Same result as mhc_sinkhorn_bwd, for callers that cannot supply a workspace at all: a plug-in
+ * inside a host that owns every byte of device memory and exposes no allocator, or a caller that
+ * may not use cudaMalloc where it runs.  (No counterpart in AndreSlavescu/mHC.cu, whose bindings
+ * allocate freely.)  The scratch is a fixed array in the library image, so
+ *   - the problem must fit: mhc_workspace_bytes(MHC_OP_SINKHORN_BWD, batch, n, 0, iters, MHC_F32)
+ *     <= mhc_sinkhorn_bwd_noalloc_capacity() (1 MiB), otherwise MHC_ERR_LIMIT and nothing runs;
+ *   - every GPU that loads the library holds that array until the process ends;
+ *   - all calls on one GPU share it: calls that overlap on the device race, run them one after
+ *     the other (the contents left by one call never influence the next);
+ *   - the first call on each device looks up the array's device address, so make that first call
+ *     outside of any stream capture.
+ * The call itself allocates nothing and calls no allocating routine. */
+int mhc_sinkhorn_bwd_noalloc(float* d_inp, const float* grad_out, const float* inp, int64_t batch,
+                             int n, int iters, float eps, mhc_stream_t stream);
+
+/* Bytes of built-in scratch behind mhc_sinkhorn_bwd_noalloc. */
+size_t mhc_sinkhorn_bwd_noalloc_capacity(void);
+
 /* ---------------------------------------------------------------------------------------------
  * RMSNorm over the last axis of a bf16 [B, C] tensor with a bf16 weight:
  * out = inp / sqrt(mean(inp^2) + eps) * weight; rms [B] fp32 is saved for the backward.

@@ -30,6 +30,8 @@ SIGNATURES = {
     "mhc_static_bwd": (_i, [_p] * 13 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_sinkhorn_fwd": (_i, [_p, _p, _l, _i, _i, _f, _p]),
     "mhc_sinkhorn_bwd": (_i, [_p, _p, _p, _l, _i, _i, _f, _p, _z, _p]),
+    "mhc_sinkhorn_bwd_noalloc": (_i, [_p, _p, _p, _l, _i, _i, _f, _p]),
+    "mhc_sinkhorn_bwd_noalloc_capacity": (_z, []),
     "mhc_rmsnorm_fwd": (_i, [_p, _p, _p, _p, _l, _l, _f, _p]),
     "mhc_rmsnorm_bwd": (_i, [_p] * 6 + [_l, _l, _p, _z, _p]),
 }

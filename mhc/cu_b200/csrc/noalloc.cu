@@ -1,0 +1,69 @@
+// mhc_sinkhorn_bwd_noalloc: the Sinkhorn-Knopp backward for callers that have no way to hand over
+// scratch memory.  Everything else in this library takes a caller-provided workspace; a host that
+// owns all device memory itself and gives a plug-in no allocator (or that must not call
+// cudaMalloc on its hot path because the call synchronises the device) cannot provide one.  For
+// those callers the scratch of this one op lives in a fixed array inside the library image.
+//
+// The array is part of the module: every GPU that loads libmhc_b200.so carries kScratchBytes of
+// it until the process exits.  All calls on a device share it, so two calls that overlap on the
+// GPU (different streams, or different host threads) race on it; callers serialise them.
+#include "../../../include/mhc_b200.h"
+
+#include <mutex>
+
+#include "kernels.h"
+
+namespace {
+
+constexpr size_t kScratchBytes = size_t(1) << 20;   // 1 MiB: e.g. 1024 4x4 matrices at 20 iterations
+constexpr int kMaxDevices = 64;
+
+// Device-side scratch.  In host code this name is only a handle for the runtime, not an address a
+// kernel could use: the real device address is looked up with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_scratch[kScratchBytes];
+
+std::mutex g_mu;
+void* g_scratch_ptr[kMaxDevices] = {};   // per-device address of g_scratch, filled on first use
+
+// Address of g_scratch on the current device (looked up once per device, with that device current).
+cudaError_t scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_scratch);
+        if (e != cudaSuccess) return e;
+        g_scratch_ptr[dev] = p;
+    }
+    *out = g_scratch_ptr[dev];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t mhc_sinkhorn_bwd_noalloc_capacity(void) { return kScratchBytes; }
+
+int mhc_sinkhorn_bwd_noalloc(float* d_inp, const float* grad_out, const float* inp, int64_t batch,
+                             int n, int iters, float eps, mhc_stream_t stream) {
+    if (batch < 0 || n < 1 || n > mhc::kMaxStreams || iters < 0) return MHC_ERR_BAD_SHAPE;
+    if (!d_inp || !grad_out || !inp) return MHC_ERR_NULL_POINTER;
+    // same sizing rule as mhc_workspace_bytes(MHC_OP_SINKHORN_BWD, ...)
+    const size_t need = mhc_workspace_bytes(MHC_OP_SINKHORN_BWD, batch, n, 0, iters, MHC_F32);
+    if (need == (size_t)-1) return MHC_ERR_BAD_SHAPE;
+    if (need > kScratchBytes) return MHC_ERR_LIMIT;
+    void* scratch = nullptr;
+    if (scratch_address(&scratch) != cudaSuccess || scratch == nullptr) return MHC_ERR_CUDA;
+    // Nothing in the scratch has to start at zero: the forward sweep writes every denominator the
+    // reverse sweep reads, so leftovers of an earlier call are never observed.
+    const cudaError_t e = mhc::launch_sinkhorn_bwd(d_inp, grad_out, inp, scratch, batch, n, iters,
+                                                   eps, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return MHC_ERR_CUDA;
+    return MHC_OK;
+}
+
+}  // extern "C"
