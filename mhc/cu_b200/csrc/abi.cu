@@ -88,7 +88,7 @@ struct DynBwdWs {
     bool mma;
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
         mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
-        nblk = coeffs_dyn_bwd_blocks(d);
+        nblk = d.n <= 8 ? coeffs_thread_blocks(d) : coeffs_dyn_bwd_blocks(d);
         ntb = mma ? dx_mma_token_blocks(d) : dx_token_blocks(d);
         const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
         rec = c.take<float>(mma ? (size_t)d.B * bwd_mma_record_floats(d) : 0);
@@ -101,7 +101,9 @@ struct DynBwdWs {
         partials = c.take<float>((size_t)nblk * (d.K() + 3));
         dw_part = c.take<float>((size_t)ntb * d.C);
         const int G = group_lanes(d.n) < 2 ? 2 : group_lanes(d.n);
-        den = c.take_bytes((size_t)d.B * G * 2 * (size_t)iters * den_elem(dtype));
+        const size_t per_token =
+            d.n <= 8 ? (size_t)coeffs_thread_den_per_token(d, iters) : (size_t)G * 2 * iters;
+        den = c.take_bytes((size_t)d.B * per_token * den_elem(dtype));
     }
 };
 
@@ -169,14 +171,23 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
                   float eps, int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     DynBwdWs ws(c, d, iters, dtype);
-    MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
-                                 H_post, 1, rms, d, s));
+    if (bwd_reduce_staged_supported(d, sizeof(T)))
+        MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
+                                            H_pre, H_post, 1, rms, nullptr, d, s));
+    else
+        MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
+                                     H_post, 1, rms, d, s));
     MmaBwdOut mo;
     if (ws.mma) {
         mo.rec = ws.rec; mo.dprb = ws.dprb; mo.dprT = ws.dprT; mo.M = M; mo.rms = rms; mo.c2 = ws.c2;
     }
-    MHC_TRY(launch_coeffs_dyn_bwd(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
-                                  alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, mo, s));
+    if (d.n <= 8)
+        MHC_TRY(launch_coeffs_dyn_bwd_thread(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj,
+                                             rms_h, alpha, bias, ws.den, d, iters, eps,
+                                             dtype == MHC_F32, mo, s));
+    else
+        MHC_TRY(launch_coeffs_dyn_bwd(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
+                                      alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, mo, s));
     if constexpr (std::is_same<T, bf16>::value) {
         if (ws.mma) {
             MHC_TRY(launch_dx_mma((bf16*)dx, ws.dw_part, (const bf16*)x, (const bf16*)dy,
@@ -217,8 +228,12 @@ int static_bwd_t(void* dx, float* d_w, float* d_H_pre, float* d_H_post, float* d
                  int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     StaticBwdWs ws(c, d, iters, dtype);
-    MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq, 0,
-                                 rms, d, s));
+    if (bwd_reduce_staged_supported(d, sizeof(T)))
+        MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
+                                            hp, hq, 0, rms, nullptr, d, s));
+    else
+        MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq,
+                                     0, rms, d, s));
     MHC_TRY(launch_coeffs_static_bwd(d_H_pre, d_H_post, d_H_res, ws.dH, hp, hq, H_res, ws.den, d,
                                      iters, eps, dtype == MHC_F32, s));
     MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq,

@@ -1,0 +1,161 @@
+// Per-token backward algebra with ONE THREAD PER TOKEN (n <= 8): the token's n x n matrices live
+// in that thread's registers, so the 2*iters Sinkhorn steps need no shuffles and the n rows
+// (columns) of a step are independent instruction chains.  A warp handles 32 tokens; its
+// token-summed outputs (d_bias, d_alpha terms) are added in shared memory in token order and
+// leave the block as one partial row, so the final sums are bit-reproducible.
+//
+// Same inputs / outputs as coeffs_dyn_bwd_kernel in coeffs.cu (which remains for n > 8).
+#include "kernels.h"
+#include "sinkhorn.cuh"
+
+namespace mhc {
+
+namespace {
+
+constexpr int kTokThreads = 32;
+
+template <int MAXN, typename A>
+__global__ void __launch_bounds__(kTokThreads)
+coeffs_dyn_bwd_thread_kernel(float* __restrict__ dpr, float* __restrict__ qq,
+                             float* __restrict__ partials, const float* __restrict__ dH,
+                             const float* __restrict__ H_pre, const float* __restrict__ H_post,
+                             const float* __restrict__ proj, const float* __restrict__ rms_h,
+                             const float* __restrict__ alpha, const float* __restrict__ bias,
+                             A* __restrict__ den_ws, int64_t B, int n, int64_t nC, int iters,
+                             float eps, MmaBwdOut mo) {
+    extern __shared__ float sm[];   // [kTokThreads][K+3]
+    const int K = 2 * n + n * n;
+    const int KP = K + 3;
+    const int K8P = (K + 7) / 8 * 8;
+    const int64_t Bp = (B + 15) / 16 * 16;
+    const int64_t tok = (int64_t)blockIdx.x * kTokThreads + threadIdx.x;
+    const bool act = tok < B;
+    float* smt = sm + threadIdx.x * KP;
+    for (int k = 0; k < KP; ++k) smt[k] = 0.f;
+
+    if (act) {
+        const float* pj = proj + tok * K;
+        const float* dh = dH + tok * K;
+        const A a0 = A(alpha[0]), a1 = A(alpha[1]), a2 = A(alpha[2]);
+        A y[MAXN][MAXN], d[MAXN][MAXN];
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+            for (int j = 0; j < MAXN; ++j) {
+                const bool in = (i < n) && (j < n);
+                const int k = 2 * n + i * n + j;
+                y[i][j] = in ? sk_exp<A>(a2 * A(pj[k]) + A(bias[k])) : A(0);
+                d[i][j] = in ? A(dh[k]) : A(0);
+            }
+        A* den = den_ws + tok * 2 * (int64_t)iters * MAXN;
+        sk_forward_thread<MAXN, A, true>(y, n, iters, A(eps), den);
+        sk_backward_thread<MAXN, A>(d, y, n, iters, den);
+
+        const A r = A(rms_h[tok]);
+        const A rinv = A(1) / r;
+        float* dpo = dpr + tok * K;
+        A qacc = A(0), dal0 = A(0), dal1 = A(0), dal2 = A(0);
+        const int RS = (n * n + 2 * n + 3 + 3) / 4 * 4;
+        float* rc = (mo.rec != nullptr) ? mo.rec + tok * RS : nullptr;
+        for (int i = 0; i < n; ++i) {
+            const A hp = A(H_pre[tok * n + i]), hq = A(H_post[tok * n + i]);
+            const A pp = A(pj[i]), pq = A(pj[n + i]);
+            const A dtp = A(dh[i]) * hp * (A(1) - hp);
+            const A dtq = A(dh[n + i]) * hq * (A(1) - hq * A(0.5));
+            const A vp = a0 * dtp * rinv, vq = a1 * dtq * rinv;
+            dpo[i] = (float)vp;
+            dpo[n + i] = (float)vq;
+            smt[i] = (float)dtp;
+            smt[n + i] = (float)dtq;
+            qacc += vp * pp + vq * pq;
+            dal0 += dtp * pp;
+            dal1 += dtq * pq;
+            if (rc != nullptr) {
+                rc[n * n + i] = (float)hp;
+                rc[n * n + n + i] = (float)hq;
+                mo.dprb[tok * K8P + i] = __float2bfloat16_rn((float)vp);
+                mo.dprb[tok * K8P + n + i] = __float2bfloat16_rn((float)vq);
+                mo.dprT[(int64_t)i * Bp + tok] = __float2bfloat16_rn((float)vp);
+                mo.dprT[(int64_t)(n + i) * Bp + tok] = __float2bfloat16_rn((float)vq);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAXN; ++i)
+#pragma unroll
+            for (int j = 0; j < MAXN; ++j) {
+                if (i < n && j < n) {
+                    const int k = 2 * n + i * n + j;
+                    const A dtr = d[i][j] * y[i][j];   // dE * E (E rebuilt by the reverse sweep)
+                    const A pv = A(pj[k]);
+                    const A v = a2 * dtr * rinv;
+                    dpo[k] = (float)v;
+                    smt[k] = (float)dtr;
+                    qacc += v * pv;
+                    dal2 += dtr * pv;
+                    if (rc != nullptr) {
+                        rc[j * n + i] = mo.M[tok * n * n + i * n + j];   // MT[j][i] = M[i][j]
+                        mo.dprb[tok * K8P + k] = __float2bfloat16_rn((float)v);
+                        mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn((float)v);
+                    }
+                }
+            }
+        const float qv = (float)(qacc / (A(nC) * r));
+        qq[tok] = qv;
+        smt[K] = (float)dal0;
+        smt[K + 1] = (float)dal1;
+        smt[K + 2] = (float)dal2;
+        if (rc != nullptr) {
+            rc[n * n + 2 * n] = 1.f / mo.rms[tok];
+            rc[n * n + 2 * n + 1] = mo.c2[tok];
+            rc[n * n + 2 * n + 2] = qv;
+            for (int k = K; k < K8P; ++k) {
+                mo.dprb[tok * K8P + k] = __float2bfloat16_rn(0.f);
+                mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn(0.f);
+            }
+        }
+    } else if (mo.rec != nullptr && tok < Bp) {
+        // padding tokens of the k-major bf16 copy
+        for (int k = 0; k < K8P; ++k) mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();
+    for (int k = threadIdx.x; k < KP; k += kTokThreads) {
+        float t = 0.f;
+        for (int g = 0; g < kTokThreads; ++g) t += sm[g * KP + k];
+        partials[(int64_t)blockIdx.x * KP + k] = t;
+    }
+}
+
+}  // namespace
+
+int coeffs_thread_blocks(Dims d) {
+    const int64_t Bp = (d.B + 15) / 16 * 16;
+    return (int)((Bp + kTokThreads - 1) / kTokThreads);
+}
+
+// floats / doubles of Sinkhorn denominators per token
+int coeffs_thread_den_per_token(Dims d, int iters) { return 2 * iters * (d.n <= 4 ? 4 : 8); }
+
+cudaError_t launch_coeffs_dyn_bwd_thread(float* dpr, float* qq, float* partials, const float* dH,
+                                         const float* H_pre, const float* H_post,
+                                         const float* proj, const float* rms_h,
+                                         const float* alpha, const float* bias, void* den_ws,
+                                         Dims d, int iters, float eps, bool use_double,
+                                         MmaBwdOut mo, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (d.n > 8) return cudaErrorNotSupported;
+    const unsigned grid = (unsigned)coeffs_thread_blocks(d);
+    const size_t smem = (size_t)kTokThreads * (d.K() + 3) * sizeof(float);
+#define MHC_CT(MAXN_, A_)                                                                          \
+    coeffs_dyn_bwd_thread_kernel<MAXN_, A_><<<grid, kTokThreads, smem, s>>>(                       \
+        dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (A_*)den_ws, d.B, d.n,     \
+        d.nC(), iters, eps, mo)
+    if (d.n <= 4) {
+        if (use_double) MHC_CT(4, double); else MHC_CT(4, float);
+    } else {
+        if (use_double) MHC_CT(8, double); else MHC_CT(8, float);
+    }
+#undef MHC_CT
+    return launched();
+}
+
+}  // namespace mhc

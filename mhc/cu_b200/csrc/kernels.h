@@ -61,6 +61,15 @@ cudaError_t launch_coeffs_dyn_bwd(float* dpr, float* qq, float* partials, const 
                                   const float* rms_h, const float* alpha, const float* bias,
                                   void* den_ws, Dims d, int iters, float eps, bool use_double,
                                   MmaBwdOut mma, cudaStream_t s);
+// coeffs_thread.cu: the same backward algebra with one thread per token (n <= 8)
+int coeffs_thread_blocks(Dims d);                       // rows of `partials` it writes
+int coeffs_thread_den_per_token(Dims d, int iters);     // den_ws elements per token
+cudaError_t launch_coeffs_dyn_bwd_thread(float* dpr, float* qq, float* partials, const float* dH,
+                                         const float* H_pre, const float* H_post,
+                                         const float* proj, const float* rms_h,
+                                         const float* alpha, const float* bias, void* den_ws,
+                                         Dims d, int iters, float eps, bool use_double,
+                                         MmaBwdOut mma, cudaStream_t s);
 cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float* M,
                                      const float* H_pre, const float* H_post, const float* H_res,
                                      int n, int iters, float eps, bool use_double, cudaStream_t s);
@@ -129,6 +138,13 @@ template <typename T>
 cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
                                   const float* H_post, const float* M, int* status, Dims d,
                                   float eps, cudaStream_t s);
+
+// ---- mix_bwd.cu: backward pass A with the token's x and dy rows staged by bulk async copies ---
+bool bwd_reduce_staged_supported(Dims d, size_t elem_bytes);
+template <typename T>
+cudaError_t launch_bwd_reduce_staged(float* dH, float* c2, const T* x, const T* g, const bf16* w,
+                                     const float* H_pre, const float* H_post, int coef_stride,
+                                     const float* rms, int* status, Dims d, cudaStream_t s);
 
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,
