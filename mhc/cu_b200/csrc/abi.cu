@@ -81,15 +81,17 @@ struct DynFwdWs {
 };
 
 struct DynBwdWs {
-    float *dH, *c2, *dpr, *qq, *partials, *dw_part, *rec;
+    float *dH, *c2, *dpr, *qq, *partials, *dw_part, *rec, *dphi_part;
     bf16 *dprb, *dprT;
     void* den;
     int nblk, ntb;
-    bool mma;
+    bool mma, fused;
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
         mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
         nblk = d.n <= 8 ? coeffs_thread_blocks(d) : coeffs_dyn_bwd_blocks(d);
-        ntb = mma ? dx_mma_token_blocks(d) : dx_token_blocks(d);
+        fused = mma && bwd_fused_supported(d);
+        ntb = fused ? bwd_fused_token_blocks(d) : (mma ? dx_mma_token_blocks(d) : dx_token_blocks(d));
+        dphi_part = c.take<float>(fused && ntb > 1 ? (size_t)ntb * d.K() * d.nC() : 0);
         const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
         rec = c.take<float>(mma ? (size_t)d.B * bwd_mma_record_floats(d) : 0);
         dprb = c.take<bf16>(mma ? (size_t)d.B * bwd_mma_kp(d) : 0);
@@ -189,7 +191,11 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
         MHC_TRY(launch_coeffs_dyn_bwd(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
                                       alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32, mo, s));
     if constexpr (std::is_same<T, bf16>::value) {
-        if (ws.mma) {
+        if (ws.fused) {
+            MHC_TRY(launch_dx_dphi_fused((bf16*)dx, d_phi, ws.dphi_part, ws.dw_part, (const bf16*)x,
+                                         (const bf16*)dy, (const bf16*)w, ws.rec, ws.dprb, ws.dprT,
+                                         (const bf16*)phi, d, s));
+        } else if (ws.mma) {
             MHC_TRY(launch_dx_mma((bf16*)dx, ws.dw_part, (const bf16*)x, (const bf16*)dy,
                                   (const bf16*)w, ws.rec, ws.dprb, (const bf16*)phi, d, s));
             MHC_TRY(launch_dphi_mma(d_phi, (const bf16*)x, ws.dprT, d, s));

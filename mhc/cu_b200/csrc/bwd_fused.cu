@@ -1,0 +1,378 @@
+// bf16 backward, pass B, fused: one sweep over x and dy produces dx, the token-partial d_phi and
+// the token-partial d_weight.
+//
+//   dx[b,j,c]   = sum_i M[i,j] g[i,c] + H_pre[j] da[c] - qq x[j,c] + sum_k dpr[b,k] phi[k, jC+c]
+//   dphi[k,jC+c] += sum_b dpr[b,k] x[b,j,c]          dw[c] += (sum_i H_post[i] g[i,c]) a[c] / rho
+//
+// Block = 4 warps, one block of 32 columns (of all N streams) and a range of token groups
+// (16 tokens each).  Per group the [16 tokens x N streams x 32 columns] tiles of x and dy and the
+// 16 token records are brought into shared memory with cp.async, double buffered, so the next
+// group's loads are in flight while this one is computed.  Warp w owns columns [8w, 8w+8):
+//   * dpr x phi  on mma.sync.m16n8k16 (+k8): A = dpr (16 tokens x K), B = phi fragments held in
+//     registers for the whole block; the accumulator of thread (g,q) is (tokens g, g+8) x
+//     (columns 2q, 2q+1), and the same thread finishes those outputs element-wise;
+//   * dpr^T x x  on mma.sync as well: A = dpr^T (K x 16 tokens), B = the x tile read with
+//     ldmatrix.trans (token pairs packed), accumulators stay in registers across the token loop.
+// x and dy are read once; dx is written once; d_phi leaves as one partial per token range and is
+// added up in a fixed order by dphi_sum_kernel.
+//
+// Takes over the eager GEMMs d_x_flat = d_p @ phi and d_phi = d_p^T @ x_flat of the reference's
+// dynamic backward (src/python/mhc/ops.py:330-349) and its stream_distribute_mix_backward /
+// stream_aggregate_backward / rmsnorm_backward kernels (src/csrc/kernels/stream_ops.cuh:644-997,
+// src/csrc/kernels/rmsnorm.cuh:233-306).
+#include "kernels.h"
+
+namespace mhc {
+
+namespace {
+
+__device__ __forceinline__ void f_mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void f_mma_1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
+        "{%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(b0));
+}
+// two 8x8 b16 matrices, transposed on the way: thread (g,q) gets rows (2q, 2q+1) of column g
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, const void* row_ptr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n"
+                 : "=r"(r0), "=r"(r1)
+                 : "r"((uint32_t)__cvta_generic_to_shared(row_ptr)));
+}
+__device__ __forceinline__ void f_cp_async16(void* dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst_smem)),
+                 "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void f_cp_async_commit() {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int NKEEP>
+__device__ __forceinline__ void f_cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(NKEEP) : "memory");
+}
+__device__ __forceinline__ uint32_t f_ldg_u32(const bf16* p) {
+    return *reinterpret_cast<const uint32_t*>(p);
+}
+
+constexpr int kFWarps = 4;
+constexpr int kFCols = 32;
+constexpr int kFTok = 16;
+
+template <int N>
+struct FusedCfg {
+    static constexpr int K = 2 * N + N * N;
+    static constexpr int KP = (K + 7) / 8 * 8;
+    static constexpr int K16 = KP / 16;
+    static constexpr int K8 = (KP % 16) ? 1 : 0;
+    static constexpr int MT = (KP + 15) / 16;                       // m16 tiles of d_phi rows
+    static constexpr int RS = (N * N + 2 * N + 3 + 3) / 4 * 4;      // floats per token record
+    static constexpr int TOKB = N * kFCols * 2 + 16;                // padded bytes per tile token
+    static constexpr int TILEB = kFTok * TOKB;                      // bytes per tile
+    static constexpr int RECB = kFTok * RS * 4;                     // bytes of the 16 records
+    static constexpr int BUFB = 2 * TILEB + RECB;                   // one pipeline stage
+};
+
+template <int N>
+__global__ void __launch_bounds__(kFWarps * 32, 3)
+dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __restrict__ dw_part,
+               const bf16* __restrict__ x, const bf16* __restrict__ gy,
+               const bf16* __restrict__ w, const float* __restrict__ rec,
+               const bf16* __restrict__ dprb, const bf16* __restrict__ dprT,
+               const bf16* __restrict__ phi, int64_t B, int64_t Bp, int64_t C,
+               int groups_per_block) {
+    using Cfg = FusedCfg<N>;
+    constexpr int K = Cfg::K, KP = Cfg::KP, K16 = Cfg::K16, K8 = Cfg::K8, MT = Cfg::MT,
+                  RS = Cfg::RS, TOKB = Cfg::TOKB, TILEB = Cfg::TILEB, BUFB = Cfg::BUFB;
+    extern __shared__ __align__(128) unsigned char smem[];
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int64_t c0 = (int64_t)blockIdx.x * kFCols;
+    const int64_t nC = (int64_t)N * C;
+    const int64_t cw = c0 + 8 * warp;          // first of this warp's 8 columns
+    const bool colin = cw < C;                 // C is a multiple of 8
+    const int64_t ngroups = (B + kFTok - 1) / kFTok;
+    const int64_t group0 = (int64_t)blockIdx.y * groups_per_block;
+    int64_t gend = group0 + groups_per_block;
+    if (gend > ngroups) gend = ngroups;
+
+    // ---- phi fragments of this warp's columns, all streams: B operand of dpr x phi ------------
+    // lane (g,q) supplies column cw+g, reduction rows (2q,2q+1), (2q+8,2q+9) per k16 step.
+    uint32_t fb[N][2 * K16 + K8];
+    {
+        auto pair = [&](int j, int k) -> uint32_t {
+            uint32_t lo = 0, hi = 0;
+            if (colin) {
+                const bf16* base = phi + (int64_t)j * C + cw + g;
+                if (k < K) lo = *reinterpret_cast<const uint16_t*>(base + (int64_t)k * nC);
+                if (k + 1 < K) hi = *reinterpret_cast<const uint16_t*>(base + (int64_t)(k + 1) * nC);
+            }
+            return lo | (hi << 16);
+        };
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+#pragma unroll
+            for (int s = 0; s < K16; ++s) {
+                fb[j][2 * s] = pair(j, 16 * s + 2 * q);
+                fb[j][2 * s + 1] = pair(j, 16 * s + 2 * q + 8);
+            }
+            if (K8) fb[j][2 * K16] = pair(j, 16 * K16 + 2 * q);
+        }
+    }
+    float wv[2] = {0.f, 0.f};
+    if (colin) {
+        const uint32_t ww = f_ldg_u32(w + cw + 2 * q);
+        wv[0] = bf16_lo(ww);
+        wv[1] = bf16_hi(ww);
+    }
+    float dwacc[2] = {0.f, 0.f};
+    float pacc[MT][N][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int j = 0; j < N; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pacc[m][j][e] = 0.f;
+
+    // ---- asynchronous staging of one token group ------------------------------------------------
+    auto prefetch = [&](int64_t grp, int buf) {
+        unsigned char* base = smem + (size_t)buf * BUFB;
+        // x and dy tiles: 16 tokens x N streams x 4 chunks of 8 columns
+        for (int c = tid; c < kFTok * N * 4; c += kFWarps * 32) {
+            const int part = c & 3, j = (c >> 2) % N, t = c / (4 * N);
+            const int64_t tok = grp * kFTok + t;
+            const bool in = (tok < B) && (c0 + 8 * part < C);
+            const int64_t off = (in ? tok : 0) * nC + (int64_t)j * C + (in ? c0 + 8 * part : 0);
+            unsigned char* d = base + t * TOKB + j * (kFCols * 2) + part * 16;
+            f_cp_async16(d, x + off, in ? 16u : 0u);
+            f_cp_async16(d + TILEB, gy + off, in ? 16u : 0u);
+        }
+        // the 16 token records
+        for (int c = tid; c < kFTok * (RS / 4); c += kFWarps * 32) {
+            const int part = c % (RS / 4), t = c / (RS / 4);
+            const int64_t tok = grp * kFTok + t;
+            const bool in = tok < B;
+            f_cp_async16(base + 2 * TILEB + (t * RS + part * 4) * 4,
+                         rec + (in ? tok : 0) * RS + part * 4, in ? 16u : 0u);
+        }
+        f_cp_async_commit();
+    };
+
+    int buf = 0;
+    if (group0 < gend) prefetch(group0, 0);
+    for (int64_t grp = group0; grp < gend; ++grp) {
+        const bool more = grp + 1 < gend;
+        if (more) prefetch(grp + 1, buf ^ 1);
+
+        const int64_t tok[2] = {grp * kFTok + g, grp * kFTok + g + 8};
+        const bool tv[2] = {tok[0] < B, tok[1] < B};
+        // A fragments: dpr (token major) for dpr x phi, dpr^T (k major) for dpr^T x x
+        uint32_t a[K16][4], a8[2] = {0u, 0u};
+        {
+            const bf16* d0 = dprb + (tv[0] ? tok[0] : 0) * KP;
+            const bf16* d1 = dprb + (tv[1] ? tok[1] : 0) * KP;
+#pragma unroll
+            for (int s = 0; s < K16; ++s) {
+                a[s][0] = tv[0] ? f_ldg_u32(d0 + 16 * s + 2 * q) : 0u;
+                a[s][1] = tv[1] ? f_ldg_u32(d1 + 16 * s + 2 * q) : 0u;
+                a[s][2] = tv[0] ? f_ldg_u32(d0 + 16 * s + 2 * q + 8) : 0u;
+                a[s][3] = tv[1] ? f_ldg_u32(d1 + 16 * s + 2 * q + 8) : 0u;
+            }
+            if (K8) {
+                a8[0] = tv[0] ? f_ldg_u32(d0 + 16 * K16 + 2 * q) : 0u;
+                a8[1] = tv[1] ? f_ldg_u32(d1 + 16 * K16 + 2 * q) : 0u;
+            }
+        }
+        uint32_t at[MT][4];
+        {
+            const int64_t ta = grp * kFTok + 2 * q;   // padded tokens of dprT are zero
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+                const int r0 = 16 * m + g, r1 = r0 + 8;
+                at[m][0] = (r0 < KP) ? f_ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
+                at[m][1] = (r1 < KP) ? f_ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
+                at[m][2] = (r0 < KP) ? f_ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
+                at[m][3] = (r1 < KP) ? f_ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
+            }
+        }
+
+        if (more) f_cp_async_wait<1>(); else f_cp_async_wait<0>();
+        __syncthreads();   // every thread's copies of this stage have landed
+
+        const unsigned char* xs = smem + (size_t)buf * BUFB;
+        const unsigned char* gs = xs + TILEB;
+        const float* rs = reinterpret_cast<const float*>(xs + 2 * TILEB);
+
+        // ---- d_phi: dpr^T (K x 16 tokens) times the x tile (16 tokens x 8 columns) per stream ---
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+            uint32_t b0, b1;
+            // lanes 0-7 address tokens 0-7, lanes 8-15 tokens 8-15 (the other lanes are ignored)
+            ldmatrix_x2_trans(b0, b1, xs + (lane & 15) * TOKB + j * (kFCols * 2) + warp * 16);
+#pragma unroll
+            for (int m = 0; m < MT; ++m)
+                f_mma_16816(pacc[m][j], at[m][0], at[m][1], at[m][2], at[m][3], b0, b1);
+        }
+
+        // ---- dx: dpr x phi on the tensor cores, all streams: tacc[j][0..1] -> token g,
+        //      tacc[j][2..3] -> token g+8, columns (2q, 2q+1) of this warp's eight -------------------
+        float tacc[N][4];
+#pragma unroll
+        for (int j = 0; j < N; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) tacc[j][e] = 0.f;
+#pragma unroll
+            for (int s = 0; s < K16; ++s)
+                f_mma_16816(tacc[j], a[s][0], a[s][1], a[s][2], a[s][3], fb[j][2 * s],
+                            fb[j][2 * s + 1]);
+            if (K8) f_mma_1688(tacc[j], a8[0], a8[1], fb[j][2 * K16]);
+        }
+        // ---- the element-wise rest, one token at a time -------------------------------------------
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int t = g + 8 * h;
+            const float* r = rs + t * RS;
+            float xv[N][2], gv[N][2];
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const uint32_t xw = *reinterpret_cast<const uint32_t*>(
+                    xs + t * TOKB + i * (kFCols * 2) + warp * 16 + q * 4);
+                const uint32_t gw = *reinterpret_cast<const uint32_t*>(
+                    gs + t * TOKB + i * (kFCols * 2) + warp * 16 + q * 4);
+                xv[i][0] = bf16_lo(xw); xv[i][1] = bf16_hi(xw);
+                gv[i][0] = bf16_lo(gw); gv[i][1] = bf16_hi(gw);
+            }
+            float av[2] = {0.f, 0.f}, dv[2] = {0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                const float hp = r[N * N + i], hq = r[N * N + N + i];
+                av[0] = fmaf(hp, xv[i][0], av[0]); av[1] = fmaf(hp, xv[i][1], av[1]);
+                dv[0] = fmaf(hq, gv[i][0], dv[0]); dv[1] = fmaf(hq, gv[i][1], dv[1]);
+            }
+            const float c1 = r[N * N + 2 * N], c2 = r[N * N + 2 * N + 1], qq = r[N * N + 2 * N + 2];
+            float da[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                da[e] = dv[e] * wv[e] * c1 - av[e] * c2;
+                dwacc[e] = fmaf(dv[e] * c1, av[e], dwacc[e]);   // records of padding tokens are zero
+            }
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                const float hpj = r[N * N + j];
+                float o0 = fmaf(-qq, xv[j][0], fmaf(hpj, da[0], tacc[j][2 * h]));
+                float o1 = fmaf(-qq, xv[j][1], fmaf(hpj, da[1], tacc[j][2 * h + 1]));
+#pragma unroll
+                for (int i = 0; i < N; ++i) {
+                    const float mji = r[j * N + i];    // MT[j][i] = M[i][j]
+                    o0 = fmaf(mji, gv[i][0], o0);
+                    o1 = fmaf(mji, gv[i][1], o1);
+                }
+                if (tv[h] && colin)
+                    *reinterpret_cast<uint32_t*>(dx + tok[h] * nC + (int64_t)j * C + cw + 2 * q) =
+                        pack_bf16x2(o0, o1);
+            }
+        }
+        __syncthreads();   // the stage may be overwritten by the prefetch of the next iteration
+        buf ^= 1;
+    }
+
+    // ---- partial d_phi of this block's token range: rows k = 16m+g (+8), columns cw+2q, +1 -----
+    if (colin) {
+        float* dp = dphi_part + (int64_t)blockIdx.y * K * nC;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+#pragma unroll
+            for (int j = 0; j < N; ++j) {
+                const int k0 = 16 * m + g, k1 = k0 + 8;
+                const int64_t col = (int64_t)j * C + cw + 2 * q;
+                if (k0 < K)
+                    *reinterpret_cast<float2*>(dp + (int64_t)k0 * nC + col) =
+                        make_float2(pacc[m][j][0], pacc[m][j][1]);
+                if (k1 < K)
+                    *reinterpret_cast<float2*>(dp + (int64_t)k1 * nC + col) =
+                        make_float2(pacc[m][j][2], pacc[m][j][3]);
+            }
+        }
+    }
+    // ---- partial d_weight: add the eight token lanes (g) of the warp -----------------------------
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        float v = dwacc[e];
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        v += __shfl_xor_sync(0xffffffffu, v, 8);
+        v += __shfl_xor_sync(0xffffffffu, v, 16);
+        dwacc[e] = v;
+    }
+    if (g == 0 && colin) {
+        dw_part[(int64_t)blockIdx.y * C + cw + 2 * q] = dwacc[0];
+        dw_part[(int64_t)blockIdx.y * C + cw + 2 * q + 1] = dwacc[1];
+    }
+}
+
+// d_phi[i] = sum over token ranges of dphi_part[p][i], in order
+__global__ void dphi_sum_kernel(float* __restrict__ dphi, const float* __restrict__ part, int nparts,
+                                int64_t total4) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total4) return;
+    float4 t = reinterpret_cast<const float4*>(part)[i];
+    for (int p = 1; p < nparts; ++p) {
+        const float4 v = reinterpret_cast<const float4*>(part)[(int64_t)p * total4 + i];
+        t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+    }
+    reinterpret_cast<float4*>(dphi)[i] = t;
+}
+
+}  // namespace
+
+bool bwd_fused_supported(Dims d) { return d.n == 4 && d.C % 8 == 0 && d.nC() % 4 == 0; }
+
+static int fused_groups_per_block(Dims d) {
+    const int64_t colblocks = (d.C + kFCols - 1) / kFCols;
+    const int64_t groups = (d.B + kFTok - 1) / kFTok;
+    int64_t split = (3 * 148 + colblocks - 1) / colblocks;   // about three blocks per SM
+    if (split < 1) split = 1;
+    if (split > groups) split = groups;
+    return (int)((groups + split - 1) / split);
+}
+
+// number of token ranges = rows of dw_part = partial copies of d_phi
+int bwd_fused_token_blocks(Dims d) {
+    const int64_t groups = (d.B + kFTok - 1) / kFTok;
+    const int gpb = fused_groups_per_block(d);
+    return (int)((groups + gpb - 1) / gpb);
+}
+
+cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float* dw_part,
+                                 const bf16* x, const bf16* g, const bf16* w, const float* rec,
+                                 const bf16* dprb, const bf16* dprT, const bf16* phi, Dims d,
+                                 cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    if (!bwd_fused_supported(d)) return cudaErrorNotSupported;
+    using Cfg = FusedCfg<4>;
+    const int gpb = fused_groups_per_block(d);
+    const int ntb = bwd_fused_token_blocks(d);
+    const int64_t Bp = (d.B + 15) / 16 * 16;
+    const dim3 grid((unsigned)((d.C + kFCols - 1) / kFCols), (unsigned)ntb);
+    const size_t smem = 2 * (size_t)Cfg::BUFB;
+    // with a single token range the partial IS the result
+    float* part = (ntb == 1) ? dphi : dphi_part;
+    dx_dphi_kernel<4><<<grid, kFWarps * 32, smem, s>>>(dx, part, dw_part, x, g, w, rec, dprb, dprT,
+                                                        phi, d.B, Bp, d.C, gpb);
+    cudaError_t e = launched();
+    if (e != cudaSuccess || ntb == 1) return e;
+    const int64_t total4 = (int64_t)d.K() * d.nC() / 4;
+    dphi_sum_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, s>>>(dphi, dphi_part, ntb, total4);
+    return launched();
+}
+
+}  // namespace mhc

@@ -38,6 +38,20 @@ __device__ __forceinline__ void mma_1688(float (&c)[4], uint32_t a0, uint32_t a1
         : "r"(a0), "r"(a1), "r"(b0));
 }
 
+// 16-byte asynchronous copy global -> shared (Ampere-style cp.async, lands without occupying
+// registers); src_bytes = 0 writes zeros instead of reading.
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst_smem)),
+                 "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 __device__ __forceinline__ uint32_t ldg_u32(const bf16* p) {
     return *reinterpret_cast<const uint32_t*>(p);
 }
@@ -76,6 +90,9 @@ dx_mma_kernel(bf16* __restrict__ dx, float* __restrict__ dw_part, const bf16* __
                   RS = Cfg::RS;
     __shared__ __align__(16) uint32_t fragB[N][4][32][FWP];
     __shared__ float dws[kDxWarps][kDxCols];
+    // per-thread landing slots of the x / dy patches, double buffered: [buf][vector][thread]
+    extern __shared__ __align__(16) uint4 patch[];
+    constexpr int NV = 4 * N;   // vectors per patch: {x, dy} x 2 tokens x N streams
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
@@ -123,11 +140,34 @@ dx_mma_kernel(bf16* __restrict__ dx, float* __restrict__ dw_part, const bf16* __
     const int64_t ngroups = (B + 15) / 16;
     const bool colin = (c0 + 8 * q) < C;   // C is a multiple of 8: whole vector in or out
 
+    // issue the asynchronous loads of one token group's patches into buffer `buf`
+    auto prefetch = [&](int64_t grp, int buf) {
+        uint4* slot = patch + (size_t)buf * NV * (kDxWarps * 32) + threadIdx.x;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const int64_t t = grp * 16 + g + 8 * h;
+            const bool ld = (t < B) && colin;
+            const int64_t base = (ld ? t : 0) * nC + (colin ? c0 + 8 * q : 0);
+#pragma unroll
+            for (int i = 0; i < N; ++i) {
+                cp_async16(slot + (size_t)((h * N + i) * 2 + 0) * (kDxWarps * 32), x + base + i * C,
+                           ld ? 16u : 0u);
+                cp_async16(slot + (size_t)((h * N + i) * 2 + 1) * (kDxWarps * 32), gy + base + i * C,
+                           ld ? 16u : 0u);
+            }
+        }
+        cp_async_commit();
+    };
+
+    int buf = 0;
+    if (group0 + warp < ngroups && warp < groups_per_block) prefetch(group0 + warp, 0);
     for (int gi = warp; gi < groups_per_block; gi += kDxWarps) {
         const int64_t grp = group0 + gi;
         if (grp >= ngroups) break;
         const int64_t tok[2] = {grp * 16 + g, grp * 16 + g + 8};
         const bool tv[2] = {tok[0] < B, tok[1] < B};
+        const bool more = (gi + kDxWarps < groups_per_block) && (grp + kDxWarps < ngroups);
+        if (more) prefetch(grp + kDxWarps, buf ^ 1);
 
         // A fragments of dpr for this token group
         uint32_t a[K16][4], a8[2] = {0u, 0u};
@@ -147,20 +187,21 @@ dx_mma_kernel(bf16* __restrict__ dx, float* __restrict__ dw_part, const bf16* __
             }
         }
 
-        // this thread's patch of x and dy: 2 tokens x N streams x 8 columns, packed bf16
+        // this thread's patch of x and dy (2 tokens x N streams x 8 columns, packed bf16) has
+        // landed in its own slots once all but the newest copy group are complete
+        if (more) cp_async_wait<1>(); else cp_async_wait<0>();
         uint4 xp[2][N], gp[2][N];
+        {
+            const uint4* slot = patch + (size_t)buf * NV * (kDxWarps * 32) + threadIdx.x;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const bool ld = tv[h] && colin;
-            const int64_t base = (tv[h] ? tok[h] : 0) * nC + c0 + 8 * q;
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int i = 0; i < N; ++i) {
-                xp[h][i] = ld ? *reinterpret_cast<const uint4*>(x + base + i * C)
-                              : make_uint4(0u, 0u, 0u, 0u);
-                gp[h][i] = ld ? *reinterpret_cast<const uint4*>(gy + base + i * C)
-                              : make_uint4(0u, 0u, 0u, 0u);
-            }
+                for (int i = 0; i < N; ++i) {
+                    xp[h][i] = slot[(size_t)((h * N + i) * 2 + 0) * (kDxWarps * 32)];
+                    gp[h][i] = slot[(size_t)((h * N + i) * 2 + 1) * (kDxWarps * 32)];
+                }
         }
+        buf ^= 1;
 
         // da and the d_weight contribution per token
         float da[2][8];
@@ -320,28 +361,40 @@ dphi_mma_kernel(float* __restrict__ dphi, const bf16* __restrict__ x,
 
     const int64_t ngroups = (B + 15) / 16;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int64_t grp = warp; grp < ngroups; grp += kDphiWarps) {
-        const int64_t t0 = grp * 16;
-        const int64_t ta = t0 + 2 * q;   // tokens ta, ta+1, ta+8, ta+9
-        uint4 xa = zero, xb = zero, xc = zero, xd = zero;
-        const bf16* xcol = x + col0 + 8 * g;
-        if (colin) {
-            if (ta < B) xa = *reinterpret_cast<const uint4*>(xcol + ta * nC);
-            if (ta + 1 < B) xb = *reinterpret_cast<const uint4*>(xcol + (ta + 1) * nC);
-            if (ta + 8 < B) xc = *reinterpret_cast<const uint4*>(xcol + (ta + 8) * nC);
-            if (ta + 9 < B) xd = *reinterpret_cast<const uint4*>(xcol + (ta + 9) * nC);
-        }
+    const bf16* xcol = x + col0 + 8 * g;
+    // operands of one token group: four x vectors (tokens ta, ta+1, ta+8, ta+9) and the A fragments
+    struct Operands {
+        uint4 xa, xb, xc, xd;
         uint32_t afr[MT16][4];
+    };
+    auto fetch = [&](int64_t grp, Operands& o) {
+        const int64_t ta = grp * 16 + 2 * q;
+        o.xa = zero; o.xb = zero; o.xc = zero; o.xd = zero;
+        if (colin) {
+            if (ta < B) o.xa = *reinterpret_cast<const uint4*>(xcol + ta * nC);
+            if (ta + 1 < B) o.xb = *reinterpret_cast<const uint4*>(xcol + (ta + 1) * nC);
+            if (ta + 8 < B) o.xc = *reinterpret_cast<const uint4*>(xcol + (ta + 8) * nC);
+            if (ta + 9 < B) o.xd = *reinterpret_cast<const uint4*>(xcol + (ta + 9) * nC);
+        }
 #pragma unroll
         for (int m = 0; m < MT16; ++m) {
             const int r0 = row0 + 16 * m + g, r1 = r0 + 8;
-            afr[m][0] = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
-            afr[m][1] = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
-            afr[m][2] = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
-            afr[m][3] = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
+            o.afr[m][0] = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
+            o.afr[m][1] = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
+            o.afr[m][2] = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
+            o.afr[m][3] = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
         }
-        const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
-        const uint32_t wc[4] = {xc.x, xc.y, xc.z, xc.w}, wd[4] = {xd.x, xd.y, xd.z, xd.w};
+    };
+    Operands cur, nxt;
+    if (warp < ngroups) fetch(warp, cur);
+    for (int64_t grp = warp; grp < ngroups; grp += kDphiWarps) {
+        // the next group's loads are in flight while this group's MMAs run
+        const bool more = grp + kDphiWarps < ngroups;
+        if (more) fetch(grp + kDphiWarps, nxt);
+        const uint32_t wa[4] = {cur.xa.x, cur.xa.y, cur.xa.z, cur.xa.w};
+        const uint32_t wb[4] = {cur.xb.x, cur.xb.y, cur.xb.z, cur.xb.w};
+        const uint32_t wc[4] = {cur.xc.x, cur.xc.y, cur.xc.z, cur.xc.w};
+        const uint32_t wd[4] = {cur.xd.x, cur.xd.y, cur.xd.z, cur.xd.w};
 #pragma unroll
         for (int p = 0; p < 4; ++p) {
             // columns 2p and 2p+1 of this thread's 8: (token ta, ta+1) and (ta+8, ta+9) pairs
@@ -349,10 +402,13 @@ dphi_mma_kernel(float* __restrict__ dphi, const bf16* __restrict__ x,
             const uint32_t b1e = prmt(wc[p], wd[p], 0x5410), b1o = prmt(wc[p], wd[p], 0x7632);
 #pragma unroll
             for (int m = 0; m < MT16; ++m) {
-                mma_16816(acc[m][2 * p], afr[m][0], afr[m][1], afr[m][2], afr[m][3], b0e, b1e);
-                mma_16816(acc[m][2 * p + 1], afr[m][0], afr[m][1], afr[m][2], afr[m][3], b0o, b1o);
+                mma_16816(acc[m][2 * p], cur.afr[m][0], cur.afr[m][1], cur.afr[m][2],
+                          cur.afr[m][3], b0e, b1e);
+                mma_16816(acc[m][2 * p + 1], cur.afr[m][0], cur.afr[m][1], cur.afr[m][2],
+                          cur.afr[m][3], b0o, b1o);
             }
         }
+        if (more) cur = nxt;
     }
     // acc[m][u][0..1] -> row 16m+g, columns 16q+u and 16q+8+u; acc[m][u][2..3] -> row 16m+g+8.
     // One m16 tile at a time goes through shared memory and is summed over the warps in order.
@@ -413,8 +469,12 @@ cudaError_t launch_dx_mma(bf16* dx, float* dw_part, const bf16* x, const bf16* g
     if (!bwd_mma_supported(d)) return cudaErrorNotSupported;
     const int gpb = dx_groups_per_block(d);
     const dim3 grid((unsigned)((d.C + kDxCols - 1) / kDxCols), (unsigned)dx_mma_token_blocks(d));
-    dx_mma_kernel<4><<<grid, kDxWarps * 32, 0, s>>>(dx, dw_part, x, g, w, rec, dprb, phi, d.B, d.C,
-                                                     gpb);
+    const size_t smem = (size_t)2 * (4 * 4) * (kDxWarps * 32) * sizeof(uint4);   // 64 KB
+    cudaError_t e = cudaFuncSetAttribute(dx_mma_kernel<4>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dx_mma_kernel<4><<<grid, kDxWarps * 32, smem, s>>>(dx, dw_part, x, g, w, rec, dprb, phi, d.B,
+                                                        d.C, gpb);
     return launched();
 }
 

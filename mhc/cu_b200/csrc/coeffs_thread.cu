@@ -22,8 +22,8 @@ coeffs_dyn_bwd_thread_kernel(float* __restrict__ dpr, float* __restrict__ qq,
                              const float* __restrict__ proj, const float* __restrict__ rms_h,
                              const float* __restrict__ alpha, const float* __restrict__ bias,
                              A* __restrict__ den_ws, int64_t B, int n, int64_t nC, int iters,
-                             float eps, MmaBwdOut mo) {
-    extern __shared__ float sm[];   // [kTokThreads][K+3]
+                             float eps, MmaBwdOut mo, int den_in_smem) {
+    extern __shared__ __align__(16) float sm[];   // [kTokThreads][K+3], then the denominators
     const int K = 2 * n + n * n;
     const int KP = K + 3;
     const int K8P = (K + 7) / 8 * 8;
@@ -47,9 +47,20 @@ coeffs_dyn_bwd_thread_kernel(float* __restrict__ dpr, float* __restrict__ qq,
                 y[i][j] = in ? sk_exp<A>(a2 * A(pj[k]) + A(bias[k])) : A(0);
                 d[i][j] = in ? A(dh[k]) : A(0);
             }
-        A* den = den_ws + tok * 2 * (int64_t)iters * MAXN;
-        sk_forward_thread<MAXN, A, true>(y, n, iters, A(eps), den);
-        sk_backward_thread<MAXN, A>(d, y, n, iters, den);
+        // Sinkhorn denominators of the forward sweep: in shared memory (one column per thread,
+        // conflict-free) when they fit, else in the global workspace
+        A* den;
+        int ds;
+        if (den_in_smem) {
+            const int off = (kTokThreads * KP * (int)sizeof(float) + 15) / 16 * 16;
+            den = reinterpret_cast<A*>(reinterpret_cast<unsigned char*>(sm) + off) + threadIdx.x;
+            ds = kTokThreads;
+        } else {
+            den = den_ws + tok * 2 * (int64_t)iters * MAXN;
+            ds = 1;
+        }
+        sk_forward_thread<MAXN, A, true>(y, n, iters, A(eps), den, ds);
+        sk_backward_thread<MAXN, A>(d, y, n, iters, den, ds);
 
         const A r = A(rms_h[tok]);
         const A rinv = A(1) / r;
@@ -144,11 +155,15 @@ cudaError_t launch_coeffs_dyn_bwd_thread(float* dpr, float* qq, float* partials,
     if (d.B == 0) return cudaSuccess;
     if (d.n > 8) return cudaErrorNotSupported;
     const unsigned grid = (unsigned)coeffs_thread_blocks(d);
-    const size_t smem = (size_t)kTokThreads * (d.K() + 3) * sizeof(float);
+    const size_t part = ((size_t)kTokThreads * (d.K() + 3) * sizeof(float) + 15) / 16 * 16;
+    const size_t den_bytes = (size_t)kTokThreads * 2 * iters * (d.n <= 4 ? 4 : 8) *
+                             (use_double ? sizeof(double) : sizeof(float));
+    const int den_in_smem = (part + den_bytes <= 48 * 1024) ? 1 : 0;
+    const size_t smem = part + (den_in_smem ? den_bytes : 0);
 #define MHC_CT(MAXN_, A_)                                                                          \
     coeffs_dyn_bwd_thread_kernel<MAXN_, A_><<<grid, kTokThreads, smem, s>>>(                       \
         dpr, qq, partials, dH, H_pre, H_post, proj, rms_h, alpha, bias, (A_*)den_ws, d.B, d.n,     \
-        d.nC(), iters, eps, mo)
+        d.nC(), iters, eps, mo, den_in_smem)
     if (d.n <= 4) {
         if (use_double) MHC_CT(4, double); else MHC_CT(4, float);
     } else {

@@ -146,6 +146,14 @@ cudaError_t launch_bwd_reduce_staged(float* dH, float* c2, const T* x, const T* 
                                      const float* H_pre, const float* H_post, int coef_stride,
                                      const float* rms, int* status, Dims d, cudaStream_t s);
 
+// ---- bwd_fused.cu: dx + partial d_phi + partial d_weight in one sweep over x and dy (bf16) -----
+bool bwd_fused_supported(Dims d);
+int bwd_fused_token_blocks(Dims d);   // rows of dw_part and partial copies of d_phi [K][nC]
+cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float* dw_part,
+                                 const bf16* x, const bf16* g, const bf16* w, const float* rec,
+                                 const bf16* dprb, const bf16* dprT, const bf16* phi, Dims d,
+                                 cudaStream_t s);
+
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,
                                int64_t C, float eps, cudaStream_t s);

@@ -123,11 +123,11 @@ __device__ __forceinline__ float sk_rcp<float>(float v) {
 template <>
 __device__ __forceinline__ double sk_rcp<double>(double v) { return 1.0 / v; }
 
-// den (optional): den[(2t) * MAXN + i] = row sum + eps of row i at iteration t,
-//                 den[(2t+1) * MAXN + j] = column sum + eps of column j.
+// den (optional), element stride ds: den[((2t) * MAXN + i) * ds] = row sum + eps of row i at
+// iteration t, den[((2t+1) * MAXN + j) * ds] = column sum + eps of column j.
 template <int MAXN, typename A, bool STORE>
 __device__ __forceinline__ void sk_forward_thread_full(A (&m)[MAXN][MAXN], int iters, A eps,
-                                                       A* den) {
+                                                       A* den, int ds) {
     // n == MAXN: no size guards, so the MAXN row (column) chains are straight-line code
     for (int t = 0; t < iters; ++t) {
         A inv[MAXN];
@@ -138,7 +138,7 @@ __device__ __forceinline__ void sk_forward_thread_full(A (&m)[MAXN][MAXN], int i
             for (int j = 1; j < MAXN; ++j) rs += m[i][j];
             const A rd = rs + eps;
             inv[i] = sk_rcp<A>(rd);
-            if (STORE) den[(2 * t) * MAXN + i] = rd;
+            if (STORE) den[((2 * t) * MAXN + i) * ds] = rd;
         }
 #pragma unroll
         for (int i = 0; i < MAXN; ++i)
@@ -151,7 +151,7 @@ __device__ __forceinline__ void sk_forward_thread_full(A (&m)[MAXN][MAXN], int i
             for (int i = 1; i < MAXN; ++i) cs += m[i][j];
             const A cd = cs + eps;
             inv[j] = sk_rcp<A>(cd);
-            if (STORE) den[(2 * t + 1) * MAXN + j] = cd;
+            if (STORE) den[((2 * t + 1) * MAXN + j) * ds] = cd;
         }
 #pragma unroll
         for (int i = 0; i < MAXN; ++i)
@@ -162,9 +162,9 @@ __device__ __forceinline__ void sk_forward_thread_full(A (&m)[MAXN][MAXN], int i
 
 template <int MAXN, typename A, bool STORE>
 __device__ __forceinline__ void sk_forward_thread(A (&m)[MAXN][MAXN], int n, int iters, A eps,
-                                                  A* den) {
+                                                  A* den, int ds = 1) {
     if (n == MAXN) {
-        sk_forward_thread_full<MAXN, A, STORE>(m, iters, eps, den);
+        sk_forward_thread_full<MAXN, A, STORE>(m, iters, eps, den, ds);
         return;
     }
     for (int t = 0; t < iters; ++t) {
@@ -180,7 +180,7 @@ __device__ __forceinline__ void sk_forward_thread(A (&m)[MAXN][MAXN], int n, int
 #pragma unroll
                 for (int j = 0; j < MAXN; ++j)
                     if (j < n) m[i][j] *= inv;
-                if (STORE) den[(2 * t) * MAXN + i] = rd;
+                if (STORE) den[((2 * t) * MAXN + i) * ds] = rd;
             }
         }
 #pragma unroll
@@ -195,7 +195,7 @@ __device__ __forceinline__ void sk_forward_thread(A (&m)[MAXN][MAXN], int n, int
 #pragma unroll
                 for (int i = 0; i < MAXN; ++i)
                     if (i < n) m[i][j] *= inv;
-                if (STORE) den[(2 * t + 1) * MAXN + j] = cd;
+                if (STORE) den[((2 * t + 1) * MAXN + j) * ds] = cd;
             }
         }
     }
@@ -204,12 +204,12 @@ __device__ __forceinline__ void sk_forward_thread(A (&m)[MAXN][MAXN], int n, int
 // Reverse sweep; d = dL/dM on entry and dL/dE on return, y = M on entry and E (rebuilt) on return.
 template <int MAXN, typename A>
 __device__ __forceinline__ void sk_backward_thread(A (&d)[MAXN][MAXN], A (&y)[MAXN][MAXN], int n,
-                                                   int iters, const A* den) {
+                                                   int iters, const A* den, int ds = 1) {
     for (int t = iters - 1; t >= 0; --t) {
 #pragma unroll
         for (int j = 0; j < MAXN; ++j) {
             if (j < n) {
-                const A cd = den[(2 * t + 1) * MAXN + j];
+                const A cd = den[((2 * t + 1) * MAXN + j) * ds];
                 const A inv = sk_rcp<A>(cd);
                 A tc = A(0);
 #pragma unroll
@@ -227,7 +227,7 @@ __device__ __forceinline__ void sk_backward_thread(A (&d)[MAXN][MAXN], A (&y)[MA
 #pragma unroll
         for (int i = 0; i < MAXN; ++i) {
             if (i < n) {
-                const A rd = den[(2 * t) * MAXN + i];
+                const A rd = den[((2 * t) * MAXN + i) * ds];
                 const A inv = sk_rcp<A>(rd);
                 A tr = A(0);
 #pragma unroll
