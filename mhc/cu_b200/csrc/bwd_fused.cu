@@ -145,25 +145,42 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
             for (int e = 0; e < 4; ++e) pacc[m][j][e] = 0.f;
 
     // ---- asynchronous staging of one token group ------------------------------------------------
+    // Each thread always copies the same chunks of a stage: x / dy chunks tid and tid+128 of the
+    // 16 x N x 4 grid (token, stream, 8-column part) and, for tid < 16*RS/4, one record chunk.
+    // Everything that does not depend on the group is computed once, here.
+    constexpr int NCHUNK = kFTok * N * 4;
+    constexpr int PER_THREAD = (NCHUNK + kFWarps * 32 - 1) / (kFWarps * 32);
+    int64_t src_off[PER_THREAD];     // element offset inside a group (token part added per group)
+    int dst_off[PER_THREAD];         // byte offset inside a tile
+    int chunk_tok[PER_THREAD];
+    bool chunk_col_in[PER_THREAD];
+#pragma unroll
+    for (int u = 0; u < PER_THREAD; ++u) {
+        const int c = tid + u * kFWarps * 32;
+        const int part = c & 3, j = (c >> 2) % N, t = c / (4 * N);
+        chunk_tok[u] = (c < NCHUNK) ? t : -1;
+        chunk_col_in[u] = (c0 + 8 * part) < C;
+        src_off[u] = (int64_t)t * nC + (int64_t)j * C + (chunk_col_in[u] ? c0 + 8 * part : 0);
+        dst_off[u] = t * TOKB + j * (kFCols * 2) + part * 16;
+    }
+    const bool has_rec = tid < kFTok * (RS / 4);
+    const int rec_tok = tid / (RS / 4), rec_part = tid % (RS / 4);
     auto prefetch = [&](int64_t grp, int buf) {
         unsigned char* base = smem + (size_t)buf * BUFB;
-        // x and dy tiles: 16 tokens x N streams x 4 chunks of 8 columns
-        for (int c = tid; c < kFTok * N * 4; c += kFWarps * 32) {
-            const int part = c & 3, j = (c >> 2) % N, t = c / (4 * N);
-            const int64_t tok = grp * kFTok + t;
-            const bool in = (tok < B) && (c0 + 8 * part < C);
-            const int64_t off = (in ? tok : 0) * nC + (int64_t)j * C + (in ? c0 + 8 * part : 0);
-            unsigned char* d = base + t * TOKB + j * (kFCols * 2) + part * 16;
-            f_cp_async16(d, x + off, in ? 16u : 0u);
-            f_cp_async16(d + TILEB, gy + off, in ? 16u : 0u);
+        const int64_t t0 = grp * kFTok;
+#pragma unroll
+        for (int u = 0; u < PER_THREAD; ++u) {
+            if (chunk_tok[u] >= 0) {
+                const bool in = (t0 + chunk_tok[u] < B) && chunk_col_in[u];
+                const int64_t off = in ? t0 * nC + src_off[u] : 0;
+                f_cp_async16(base + dst_off[u], x + off, in ? 16u : 0u);
+                f_cp_async16(base + dst_off[u] + TILEB, gy + off, in ? 16u : 0u);
+            }
         }
-        // the 16 token records
-        for (int c = tid; c < kFTok * (RS / 4); c += kFWarps * 32) {
-            const int part = c % (RS / 4), t = c / (RS / 4);
-            const int64_t tok = grp * kFTok + t;
-            const bool in = tok < B;
-            f_cp_async16(base + 2 * TILEB + (t * RS + part * 4) * 4,
-                         rec + (in ? tok : 0) * RS + part * 4, in ? 16u : 0u);
+        if (has_rec) {
+            const bool in = t0 + rec_tok < B;
+            f_cp_async16(base + 2 * TILEB + (rec_tok * RS + rec_part * 4) * 4,
+                         rec + (in ? (t0 + rec_tok) * RS : 0) + rec_part * 4, in ? 16u : 0u);
         }
         f_cp_async_commit();
     };
@@ -241,7 +258,12 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int t = g + 8 * h;
-            const float* r = rs + t * RS;
+            float r[RS];
+#pragma unroll
+            for (int u = 0; u < RS / 4; ++u) {
+                const float4 v = *reinterpret_cast<const float4*>(rs + t * RS + 4 * u);
+                r[4 * u] = v.x; r[4 * u + 1] = v.y; r[4 * u + 2] = v.z; r[4 * u + 3] = v.w;
+            }
             float xv[N][2], gv[N][2];
 #pragma unroll
             for (int i = 0; i < N; ++i) {
@@ -339,7 +361,7 @@ bool bwd_fused_supported(Dims d) { return d.n == 4 && d.C % 8 == 0 && d.nC() % 4
 static int fused_groups_per_block(Dims d) {
     const int64_t colblocks = (d.C + kFCols - 1) / kFCols;
     const int64_t groups = (d.B + kFTok - 1) / kFTok;
-    int64_t split = (3 * 148 + colblocks - 1) / colblocks;   // about three blocks per SM
+    int64_t split = (3 * 148) / colblocks;   // at most three blocks per SM: one resident wave
     if (split < 1) split = 1;
     if (split > groups) split = groups;
     return (int)((groups + split - 1) / split);
