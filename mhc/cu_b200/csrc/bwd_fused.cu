@@ -79,7 +79,10 @@ struct FusedCfg {
     static constexpr int TOKB = N * kFCols * 2 + 16;                // padded bytes per tile token
     static constexpr int TILEB = kFTok * TOKB;                      // bytes per tile
     static constexpr int RECB = kFTok * RS * 4;                     // bytes of the 16 records
-    static constexpr int BUFB = 2 * TILEB + RECB;                   // one pipeline stage
+    static constexpr int DPB = kFTok * KP * 2;                      // dpr rows of the 16 tokens
+    static constexpr int DPTB = KP * kFTok * 2;                     // dpr^T: KP rows of 16 tokens
+    static constexpr int BUFB = 2 * TILEB + RECB + DPB + DPTB;      // one pipeline stage
+    static constexpr int STAGES = 3;
 };
 
 template <int N>
@@ -92,7 +95,8 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
                int groups_per_block) {
     using Cfg = FusedCfg<N>;
     constexpr int K = Cfg::K, KP = Cfg::KP, K16 = Cfg::K16, K8 = Cfg::K8, MT = Cfg::MT,
-                  RS = Cfg::RS, TOKB = Cfg::TOKB, TILEB = Cfg::TILEB, BUFB = Cfg::BUFB;
+                  RS = Cfg::RS, TOKB = Cfg::TOKB, TILEB = Cfg::TILEB, BUFB = Cfg::BUFB,
+                  RECB = Cfg::RECB, DPB = Cfg::DPB, STAGES = Cfg::STAGES;
     extern __shared__ __align__(128) unsigned char smem[];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -182,53 +186,66 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
             f_cp_async16(base + 2 * TILEB + (rec_tok * RS + rec_part * 4) * 4,
                          rec + (in ? (t0 + rec_tok) * RS : 0) + rec_part * 4, in ? 16u : 0u);
         }
+        // A operands: dpr rows of the 16 tokens (KP/8 chunks each) and dpr^T (2 chunks per k row;
+        // its padding tokens up to Bp are zero in global memory)
+        constexpr int DPC = kFTok * (KP / 8), DPTC = KP * 2;
+        if (tid < DPC) {
+            const int t = tid / (KP / 8), part = tid % (KP / 8);
+            const bool in = t0 + t < B;
+            f_cp_async16(base + 2 * TILEB + RECB + (t * KP + part * 8) * 2,
+                         dprb + (in ? (t0 + t) * KP : 0) + part * 8, in ? 16u : 0u);
+        } else if (tid < DPC + DPTC) {
+            const int r = (tid - DPC) >> 1, part = (tid - DPC) & 1;
+            f_cp_async16(base + 2 * TILEB + RECB + DPB + (r * kFTok + part * 8) * 2,
+                         dprT + (int64_t)r * Bp + t0 + part * 8, 16u);
+        }
         f_cp_async_commit();
     };
 
+    static_assert(kFTok * (KP / 8) + KP * 2 <= kFWarps * 32, "A-operand chunks exceed the block");
     int buf = 0;
-    if (group0 < gend) prefetch(group0, 0);
+#pragma unroll
+    for (int u = 0; u < STAGES - 1; ++u)
+        if (group0 + u < gend) prefetch(group0 + u, u);
     for (int64_t grp = group0; grp < gend; ++grp) {
-        const bool more = grp + 1 < gend;
-        if (more) prefetch(grp + 1, buf ^ 1);
+        // keep STAGES-1 groups in flight ahead of the one being computed
+        if (grp + STAGES - 1 < gend) prefetch(grp + STAGES - 1, (buf + STAGES - 1) % STAGES);
+        const int64_t ahead = gend - 1 - grp;   // groups issued after this one
+        if (ahead >= 2) f_cp_async_wait<2>();
+        else if (ahead == 1) f_cp_async_wait<1>();
+        else f_cp_async_wait<0>();
+        __syncthreads();   // every thread's copies of this stage have landed
 
         const int64_t tok[2] = {grp * kFTok + g, grp * kFTok + g + 8};
         const bool tv[2] = {tok[0] < B, tok[1] < B};
-        // A fragments: dpr (token major) for dpr x phi, dpr^T (k major) for dpr^T x x
-        uint32_t a[K16][4], a8[2] = {0u, 0u};
-        {
-            const bf16* d0 = dprb + (tv[0] ? tok[0] : 0) * KP;
-            const bf16* d1 = dprb + (tv[1] ? tok[1] : 0) * KP;
-#pragma unroll
-            for (int s = 0; s < K16; ++s) {
-                a[s][0] = tv[0] ? f_ldg_u32(d0 + 16 * s + 2 * q) : 0u;
-                a[s][1] = tv[1] ? f_ldg_u32(d1 + 16 * s + 2 * q) : 0u;
-                a[s][2] = tv[0] ? f_ldg_u32(d0 + 16 * s + 2 * q + 8) : 0u;
-                a[s][3] = tv[1] ? f_ldg_u32(d1 + 16 * s + 2 * q + 8) : 0u;
-            }
-            if (K8) {
-                a8[0] = tv[0] ? f_ldg_u32(d0 + 16 * K16 + 2 * q) : 0u;
-                a8[1] = tv[1] ? f_ldg_u32(d1 + 16 * K16 + 2 * q) : 0u;
-            }
-        }
-        uint32_t at[MT][4];
-        {
-            const int64_t ta = grp * kFTok + 2 * q;   // padded tokens of dprT are zero
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                const int r0 = 16 * m + g, r1 = r0 + 8;
-                at[m][0] = (r0 < KP) ? f_ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
-                at[m][1] = (r1 < KP) ? f_ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
-                at[m][2] = (r0 < KP) ? f_ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
-                at[m][3] = (r1 < KP) ? f_ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
-            }
-        }
-
-        if (more) f_cp_async_wait<1>(); else f_cp_async_wait<0>();
-        __syncthreads();   // every thread's copies of this stage have landed
-
         const unsigned char* xs = smem + (size_t)buf * BUFB;
         const unsigned char* gs = xs + TILEB;
         const float* rs = reinterpret_cast<const float*>(xs + 2 * TILEB);
+        const bf16* dps = reinterpret_cast<const bf16*>(xs + 2 * TILEB + RECB);    // [16][KP]
+        const bf16* dpts = dps + kFTok * KP;                                        // [KP][16]
+
+        // A fragments: dpr (token major) for dpr x phi, dpr^T (k major) for dpr^T x x
+        uint32_t a[K16][4], a8[2] = {0u, 0u};
+#pragma unroll
+        for (int s = 0; s < K16; ++s) {
+            a[s][0] = f_ldg_u32(dps + g * KP + 16 * s + 2 * q);
+            a[s][1] = f_ldg_u32(dps + (g + 8) * KP + 16 * s + 2 * q);
+            a[s][2] = f_ldg_u32(dps + g * KP + 16 * s + 2 * q + 8);
+            a[s][3] = f_ldg_u32(dps + (g + 8) * KP + 16 * s + 2 * q + 8);
+        }
+        if (K8) {
+            a8[0] = f_ldg_u32(dps + g * KP + 16 * K16 + 2 * q);
+            a8[1] = f_ldg_u32(dps + (g + 8) * KP + 16 * K16 + 2 * q);
+        }
+        uint32_t at[MT][4];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const int r0 = 16 * m + g, r1 = r0 + 8;
+            at[m][0] = (r0 < KP) ? f_ldg_u32(dpts + r0 * kFTok + 2 * q) : 0u;
+            at[m][1] = (r1 < KP) ? f_ldg_u32(dpts + r1 * kFTok + 2 * q) : 0u;
+            at[m][2] = (r0 < KP) ? f_ldg_u32(dpts + r0 * kFTok + 2 * q + 8) : 0u;
+            at[m][3] = (r1 < KP) ? f_ldg_u32(dpts + r1 * kFTok + 2 * q + 8) : 0u;
+        }
 
         // ---- d_phi: dpr^T (K x 16 tokens) times the x tile (16 tokens x 8 columns) per stream ---
 #pragma unroll
@@ -305,7 +322,7 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
             }
         }
         __syncthreads();   // the stage may be overwritten by the prefetch of the next iteration
-        buf ^= 1;
+        buf = (buf + 1) % STAGES;
     }
 
     // ---- partial d_phi of this block's token range: rows k = 16m+g (+8), columns cw+2q, +1 -----
@@ -385,7 +402,7 @@ cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float*
     const int ntb = bwd_fused_token_blocks(d);
     const int64_t Bp = (d.B + 15) / 16 * 16;
     const dim3 grid((unsigned)((d.C + kFCols - 1) / kFCols), (unsigned)ntb);
-    const size_t smem = 2 * (size_t)Cfg::BUFB;
+    const size_t smem = (size_t)Cfg::STAGES * Cfg::BUFB;
     // with a single token range the partial IS the result
     float* part = (ntb == 1) ? dphi : dphi_part;
     dx_dphi_kernel<4><<<grid, kFWarps * 32, smem, s>>>(dx, part, dw_part, x, g, w, rec, dprb, dprT,
