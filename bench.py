@@ -117,6 +117,12 @@ class ClockSampler:
         return out
 
 
+def mark(msg):
+    """Progress line on stderr when MHC_BENCH_DEBUG is set (to locate a stall in a multi-rank run)."""
+    if os.environ.get("MHC_BENCH_DEBUG"):
+        print(f"[bench rank {os.environ.get('RANK', '0')}] {msg}", file=sys.stderr, flush=True)
+
+
 def make_problem(cfg, device, seed):
     from mhc.cu_b200 import synthetic
     B, n, C, dtype = cfg["B"], cfg["n"], cfg["C"], cfg["dtype"]
@@ -238,14 +244,12 @@ def main():
         saved.append({"rms": torch.empty(B, **f32), "rms_h": torch.empty(B, **f32),
                       "H_pre": torch.empty(B, n, **f32), "H_post": torch.empty(B, n, **f32),
                       "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32)})
-    # flat gradient bucket: d_phi | d_bias | d_alpha | d_rmsnorm_weight
-    nC = n * C
-    bucket = torch.zeros(K * nC + K + 3 + C + 8, **f32)
-    o = 0
-    d_phi = bucket[o:o + K * nC].view(K, nC); o += K * nC
-    d_bias = bucket[o:o + K]; o += K
-    d_alpha = bucket[o:o + 3]; o += 4        # keep the next slice 16-byte aligned
-    d_w = bucket[o:o + C]
+    # flat gradient bucket the backward writes into and the ranks all-reduce
+    from mhc.cu_b200.distributed import GradBucket
+    bucket_obj = GradBucket(n, C, dev)
+    bucket = bucket_obj.flat
+    d_phi, d_bias, d_alpha, d_w = (bucket_obj.d_phi, bucket_obj.d_bias, bucket_obj.d_alpha,
+                                   bucket_obj.d_rmsnorm_weight)
     ws_f = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag) + 16,
                        dtype=torch.uint8, device=dev)
     ws_b = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_BWD, B, n, C, iters, tag) + 16,
@@ -266,14 +270,21 @@ def main():
             s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), B, n, C, iters, eps, tag,
             ws_b.data_ptr(), ws_b.numel(), stream)
         L.check(st, "mhc_dynamic_bwd")
+
+    def reduce_grads():
+        # the one collective of the step: the flat fp32 parameter-gradient bucket
         if world > 1:
             dist.all_reduce(bucket)
 
     # kernels per step (counted by the library while one step is enqueued)
+    mark("problem built")
     k0 = lib.mhc_kernels_enqueued()
     launch_step(0, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     kernels_per_step = int(lib.mhc_kernels_enqueued() - k0)
+    reduce_grads()
+    torch.cuda.synchronize()
+    mark("first step and all-reduce done")
 
     graphs = None
     graph_note = "python launches"
@@ -282,14 +293,16 @@ def main():
             graphs = []
             for r in range(R):
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     launch_step(r, torch.cuda.current_stream().cuda_stream)
                 graphs.append(g)
-            graph_note = "cuda graph replay" + (" incl. all-reduce" if world > 1 else "")
+            graph_note = "cuda graph replay" + (" + eager all-reduce" if world > 1 else "")
         except Exception as e:  # capture of the collective can be refused; fall back to eager
             graphs = None
             graph_note = f"python launches (graph capture failed: {type(e).__name__})"
             torch.cuda.synchronize()
+
+    mark("graphs: " + graph_note)
 
     def step(i):
         r = i % R
@@ -297,6 +310,7 @@ def main():
             graphs[r].replay()
         else:
             launch_step(r, torch.cuda.current_stream().cuda_stream)
+        reduce_grads()
 
     def barrier():
         if world > 1:
@@ -306,6 +320,7 @@ def main():
     for i in range(args.warmup):
         step(i)
     barrier()
+    mark("warm-up done")
     sampler = ClockSampler(local_rank) if not args.profile else None
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
@@ -315,7 +330,12 @@ def main():
         step(i)
     e1.record()
     barrier()
+    mark("timed region done")
     ms = e0.elapsed_time(e1)
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
     if args.profile:
         if rank == 0:
             print(json.dumps({"profile_run": True, "ms_per_step": ms / args.steps,
@@ -323,18 +343,14 @@ def main():
         if world > 1:
             dist.destroy_process_group()
         return 0
-    # untimed extra load: a short timed region may fall between two 50 ms clock samples
-    t_end = time.perf_counter() + 0.4
-    i = 0
-    while time.perf_counter() < t_end:
+    # Untimed extra load so the 50 ms clock sampler surely sees the GPU busy.  The step count is
+    # derived from the rank-agreed time, so every rank issues the same number of all-reduces.
+    extra = max(1, min(20000, int(400.0 / max(ms / args.steps, 1e-3))))
+    for i in range(extra):
         step(i)
-        i += 1
     torch.cuda.synchronize()
     clocks = sampler.stop()
-    t = torch.tensor([ms], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    mark("clock sampling done")
     ms_per_step = ms / args.steps
     value = world * B * args.steps / (ms * 1e-3)
 
@@ -369,6 +385,7 @@ def main():
         dx_h.copy_(xin.grad, non_blocking=True)
         g_h.copy_(flat, non_blocking=True)
 
+    mark("e2e set up")
     e2e_steps = max(5, min(args.steps, 50))
     for i in range(3):
         e2e_step(i)

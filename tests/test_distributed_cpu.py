@@ -1,0 +1,75 @@
+"""The multi-rank host logic on CPU (gloo, world size 2): token sharding and the flat gradient
+bucket.  Each rank fills its bucket with the gradients of ITS token shard (from the CPU oracle — no
+kernels are involved here), all-reduces, and must end up with the full-batch gradients."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, out):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import oracle
+    from mhc.cu_b200 import synthetic
+    from mhc.cu_b200.distributed import GradBucket, shard_bounds
+
+    B, n, C = 11, 4, 24
+    params = synthetic.dynamic_params(n, C, seed=3, alpha=0.4, bias_scale=0.2, random_weight=True)
+    x, dy = synthetic.streams(B, n, C, seed=3)
+    lo, hi = shard_bounds(B, rank, world)
+    g = oracle.dynamic_fwd_bwd(x[lo:hi], params, dy[lo:hi], 20, 1e-5, dtype=torch.float64)
+    bucket = GradBucket(n, C, "cpu")
+    views = bucket.to_param_grads()
+    for k, v in views.items():
+        v.copy_(g["d" + k].float())
+    bucket.all_reduce()
+    full = oracle.dynamic_fwd_bwd(x, params, dy, 20, 1e-5, dtype=torch.float64)
+    worst = 0.0
+    for k, v in bucket.to_param_grads().items():
+        ref = full["d" + k]
+        worst = max(worst, float((v.double() - ref).abs().max() / ref.abs().max().clamp_min(1e-30)))
+    # dx is token-local: the shard's rows of the full dx
+    worst = max(worst, float((g["dx"] - full["dx"][lo:hi]).abs().max()))
+    out[rank] = worst
+    dist.destroy_process_group()
+
+
+def test_shard_bounds_cover_everything():
+    from mhc.cu_b200.distributed import shard_bounds
+    for total in (0, 1, 7, 1280):
+        for world in (1, 2, 3, 8):
+            spans = [shard_bounds(total, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == total
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+
+
+def test_bucket_layout():
+    from mhc.cu_b200.distributed import GradBucket
+    b = GradBucket(4, 64, "cpu")
+    assert b.d_phi.shape == (24, 256) and b.d_bias.shape == (24,) and b.d_alpha.shape == (3,)
+    assert b.d_rmsnorm_weight.shape == (64,)
+    for t in (b.d_phi, b.d_bias, b.d_alpha, b.d_rmsnorm_weight):
+        assert t.data_ptr() % 16 == 0 and t.untyped_storage().data_ptr() == b.flat.untyped_storage().data_ptr()
+    b.d_bias.fill_(2.0)
+    assert float(b.flat.sum()) == 48.0
+    assert b.all_reduce() is None           # no process group: nothing to do
+
+
+@pytest.mark.timeout(120)
+def test_two_ranks_sum_to_full_batch_gradients():
+    world = 2
+    port = 29500 + (os.getpid() % 2000)
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_worker, args=(world, port, out), nprocs=world, join=True)
+    assert len(out) == world
+    assert max(out.values()) < 1e-6, dict(out)
