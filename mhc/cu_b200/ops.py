@@ -17,7 +17,23 @@ import weakref
 import torch
 from torch.autograd import Function
 
-from . import capi
+_EXT = None
+
+
+def _ext():
+    """The C++ torch extension ``mhc_cuda`` (mhc/cu_b200/csrc/torch_ext.cpp), which allocates
+    outputs and forwards to the C ABI.  There is no Python or CPU substitute."""
+    global _EXT
+    if _EXT is None:
+        try:
+            from . import mhc_cuda
+        except ImportError as e:
+            raise ImportError(
+                "mhc_cuda extension not built: run `python -m mhc.cu_b200.build` (needs nvcc and "
+                "g++); there is no fallback path") from e
+        _EXT = mhc_cuda
+    return _EXT
+
 
 _PACK_CACHE: dict = {}
 _PACK_CACHE_MAX = 16
@@ -57,7 +73,7 @@ class SinkhornKnoppFunction(Function):
     @staticmethod
     def forward(ctx, inp, num_iters, eps):
         inp = inp.contiguous()
-        out = capi.sinkhorn_fwd(inp, num_iters, eps)
+        out = _ext().sinkhorn_knopp_fwd(inp, num_iters, eps)
         ctx.save_for_backward(inp)
         ctx.num_iters = num_iters
         ctx.eps = eps
@@ -66,7 +82,8 @@ class SinkhornKnoppFunction(Function):
     @staticmethod
     def backward(ctx, grad_output):
         (inp,) = ctx.saved_tensors
-        d_inp = capi.sinkhorn_bwd(grad_output.contiguous().float(), inp, ctx.num_iters, ctx.eps)
+        d_inp = _ext().sinkhorn_knopp_bwd(grad_output.contiguous().float(), inp, ctx.num_iters,
+                                          ctx.eps)
         return d_inp, None, None
 
 
@@ -75,14 +92,14 @@ class RMSNormFunction(Function):
     def forward(ctx, inp, weight, eps):
         inp = inp.contiguous()
         weight = weight.contiguous()
-        out, rms = capi.rmsnorm_fwd(inp, weight, eps)
+        out, rms = _ext().rmsnorm_fwd(inp, weight, eps)
         ctx.save_for_backward(inp, weight, rms)
         return out
 
     @staticmethod
     def backward(ctx, grad_output):
         inp, weight, rms = ctx.saved_tensors
-        d_inp, d_weight = capi.rmsnorm_bwd(grad_output.contiguous().bfloat16(), inp, weight, rms)
+        d_inp, d_weight = _ext().rmsnorm_bwd(grad_output.contiguous().bfloat16(), inp, weight, rms)
         return d_inp, d_weight.to(weight.dtype), None
 
 
@@ -102,10 +119,9 @@ class MHCLayerFunction(Function):
         x = x_expanded.contiguous()
         w = rmsnorm_weight.contiguous()
         H_res = H_res.contiguous()
-        y, saved = capi.static_fwd(x, w, H_pre.contiguous(), H_post.contiguous(), H_res,
-                                   sinkhorn_iters, eps)
-        ctx.save_for_backward(x, w, H_res, saved["rms"], saved["H_pre_act"], saved["H_post_act"],
-                              saved["M"])
+        y, rms, hp, hq, M = _ext().mhc_layer_fwd(x, w, H_pre.contiguous(), H_post.contiguous(),
+                                                 H_res, sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, H_res, rms, hp, hq, M)
         ctx.sinkhorn_iters = sinkhorn_iters
         ctx.eps = eps
         return y
@@ -113,11 +129,10 @@ class MHCLayerFunction(Function):
     @staticmethod
     def backward(ctx, grad_output):
         x, w, H_res, rms, hp, hq, M = ctx.saved_tensors
-        saved = {"rms": rms, "H_pre_act": hp, "H_post_act": hq, "M": M}
-        dx, g = capi.static_bwd(grad_output.contiguous().to(x.dtype), x, w, H_res, saved,
-                                ctx.sinkhorn_iters, ctx.eps)
-        return (dx, g["d_rmsnorm_weight"].to(w.dtype), g["d_H_pre"], g["d_H_post"], g["d_H_res"],
-                None, None)
+        dx, d_w, d_hp, d_hq, d_hr = _ext().mhc_layer_bwd(
+            grad_output.contiguous().to(x.dtype), x, w, H_res, rms, hp, hq, M, ctx.sinkhorn_iters,
+            ctx.eps)
+        return dx, d_w.to(w.dtype), d_hp, d_hq, d_hr, None, None
 
 
 def mhc_layer_fused(x_expanded, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters=20, eps=1e-5):
@@ -130,10 +145,9 @@ def mhc_layer_fused_inference(x_expanded, rmsnorm_weight, H_pre, H_post, H_res, 
                               eps=1e-5):
     """Forward only; nothing is saved for a backward pass."""
     x = x_expanded.to(_compute_dtype(x_expanded)).contiguous()
-    y, _ = capi.static_fwd(x, rmsnorm_weight.bfloat16().contiguous(), H_pre.float().contiguous(),
-                           H_post.float().contiguous(), H_res.float().contiguous(), sinkhorn_iters,
-                           eps, inference=True)
-    return y
+    return _ext().mhc_layer_fwd_inference(
+        x, rmsnorm_weight.bfloat16().contiguous(), H_pre.float().contiguous(),
+        H_post.float().contiguous(), H_res.float().contiguous(), sinkhorn_iters, eps)
 
 
 class MHCLayerDynamicFunction(Function):
@@ -152,9 +166,9 @@ class MHCLayerDynamicFunction(Function):
         alpha = torch.stack([torch.as_tensor(a, dtype=torch.float32, device=dev).reshape(())
                              for a in (alpha_pre, alpha_post, alpha_res)]).float()
         bias = torch.cat([b_pre.reshape(-1), b_post.reshape(-1), b_res.reshape(-1)]).float()
-        y, s = capi.dynamic_fwd(x, w, phi, alpha, bias, sinkhorn_iters, eps)
-        ctx.save_for_backward(x, w, phi, alpha, bias, s["rms"], s["rms_h"], s["H_pre"], s["H_post"],
-                              s["M"], s["proj"])
+        y, rms, rms_h, hp, hq, M, proj = _ext().mhc_layer_fwd_dynamic(x, w, phi, alpha, bias,
+                                                                      sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, phi, alpha, bias, rms, rms_h, hp, hq, M, proj)
         ctx.sinkhorn_iters = sinkhorn_iters
         ctx.eps = eps
         ctx.n = n
@@ -170,13 +184,12 @@ class MHCLayerDynamicFunction(Function):
     @staticmethod
     def backward(ctx, grad_output):
         x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj = ctx.saved_tensors
-        saved = {"rms": rms, "rms_h": rms_h, "H_pre": H_pre, "H_post": H_post, "M": M, "proj": proj}
-        dx, g = capi.dynamic_bwd(grad_output.contiguous().to(x.dtype), x, w, phi, alpha, bias, saved,
-                                 ctx.sinkhorn_iters, ctx.eps)
+        dx, d_w, d_phi, d_alpha, d_bias = _ext().mhc_layer_bwd_dynamic(
+            grad_output.contiguous().to(x.dtype), x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post,
+            M, proj, ctx.sinkhorn_iters, ctx.eps)
         n = ctx.n
         dt = ctx.param_dtypes
-        d_phi, d_alpha, d_bias = g["d_phi"], g["d_alpha"], g["d_bias"]
-        return (dx, g["d_rmsnorm_weight"].to(dt[0]),
+        return (dx, d_w.to(dt[0]),
                 d_phi[:n].to(dt[1]), d_phi[n:2 * n].to(dt[2]),
                 d_phi[2 * n:].reshape(ctx.phi_res_shape).to(dt[3]),
                 d_alpha[0].to(dt[4]), d_alpha[1].to(dt[5]), d_alpha[2].to(dt[6]),

@@ -55,3 +55,19 @@ def test_validation_happens_before_any_cuda_call(lib):
     assert lib.mhc_dynamic_fwd(*([None] * 12), 4, 4, 64, 20, 1e-5, 0, None, 0, None) == 1
     assert lib.mhc_sinkhorn_fwd(None, None, 1, 40, 20, 1e-6, None) == 2
     assert lib.mhc_rmsnorm_fwd(None, None, None, None, 4, 0, 1e-5, None) == 2
+
+
+def test_torch_extension_exports_the_reference_binding_names():
+    """mhc_cuda (the C++ torch extension) builds without a GPU and carries the nine function names
+    of the reference's pybind module (src/python/bindings.cu:544-554)."""
+    build.build_lib()
+    build.build_ext()
+    from mhc.cu_b200 import mhc_cuda
+    for name in ["sinkhorn_knopp_fwd", "sinkhorn_knopp_bwd", "rmsnorm_fwd", "rmsnorm_bwd",
+                 "mhc_layer_fwd", "mhc_layer_fwd_inference", "mhc_layer_bwd",
+                 "mhc_layer_fwd_dynamic", "mhc_layer_bwd_dynamic"]:
+        assert hasattr(mhc_cuda, name), name
+    assert mhc_cuda.abi_version() == L.lib().mhc_abi_version()
+    import torch
+    with pytest.raises(RuntimeError):           # CPU tensors are refused, nothing falls back
+        mhc_cuda.sinkhorn_knopp_fwd(torch.ones(4, 4), 3, 1e-5)
