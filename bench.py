@@ -243,7 +243,8 @@ def main():
         dxs.append(torch.empty_like(xs[-1]))
         saved.append({"rms": torch.empty(B, **f32), "rms_h": torch.empty(B, **f32),
                       "H_pre": torch.empty(B, n, **f32), "H_post": torch.empty(B, n, **f32),
-                      "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32)})
+                      "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32),
+                      "sk_den": torch.empty(B, 2 * iters, 4 if n <= 4 else 8, **f32)})
     # flat gradient bucket the backward writes into and the ranks all-reduce
     from mhc.cu_b200.distributed import GradBucket
     bucket_obj = GradBucket(n, C, dev)
@@ -259,16 +260,16 @@ def main():
         s = saved[r]
         st = lib.mhc_dynamic_fwd(
             ys[r].data_ptr(), s["rms"].data_ptr(), s["rms_h"].data_ptr(), s["H_pre"].data_ptr(),
-            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), xs[r].data_ptr(),
-            w.data_ptr(), phi.data_ptr(), alpha.data_ptr(), bias.data_ptr(), B, n, C, iters, eps, tag,
-            ws_f.data_ptr(), ws_f.numel(), stream)
+            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), s["sk_den"].data_ptr(),
+            xs[r].data_ptr(), w.data_ptr(), phi.data_ptr(), alpha.data_ptr(), bias.data_ptr(), B, n, C,
+            iters, eps, tag, ws_f.data_ptr(), ws_f.numel(), stream)
         L.check(st, "mhc_dynamic_fwd")
         st = lib.mhc_dynamic_bwd(
             dxs[r].data_ptr(), d_w.data_ptr(), d_phi.data_ptr(), d_alpha.data_ptr(), d_bias.data_ptr(),
             dys[r].data_ptr(), xs[r].data_ptr(), w.data_ptr(), phi.data_ptr(), alpha.data_ptr(),
             bias.data_ptr(), s["rms"].data_ptr(), s["rms_h"].data_ptr(), s["H_pre"].data_ptr(),
-            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), B, n, C, iters, eps, tag,
-            ws_b.data_ptr(), ws_b.numel(), stream)
+            s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), s["sk_den"].data_ptr(),
+            B, n, C, iters, eps, tag, ws_b.data_ptr(), ws_b.numel(), stream)
         L.check(st, "mhc_dynamic_bwd")
 
     def reduce_grads():

@@ -87,13 +87,16 @@ size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int d
  *   y[i,:] = sum_j M[i,j] x[j,:] + H_post[i] * (a / rho * w)
  *
  * out:  y [B,n,C] dtype;  saved for backward (all fp32): rms [B] (= rho), rms_h [B] (= r),
- *       H_pre [B,n], H_post [B,n], M [B,n,n], proj [B,K] (= p).
+ *       H_pre [B,n], H_post [B,n], M [B,n,n], proj [B,K] (= p), and sk_den
+ *       [B, 2*iters, n <= 4 ? 4 : 8]: the (sum + eps) denominators of every Sinkhorn step, which
+ *       let the backward skip re-running the forward sweep.  sk_den may be NULL (the backward then
+ *       recomputes); it is filled on the bf16 path only (fp32 streams re-run the sweep in fp64).
  * in:   x [B,n,C] dtype;  rmsnorm_weight [C] bf16;  phi [K, n*C] dtype (rows: pre, post, res);
  *       alpha [3] fp32 on the device (pre, post, res);  bias [K] fp32 (b_pre, b_post, b_res).
  * alpha lives on the device so that no host synchronisation is needed
  * (the reference reads it with .item(), src/python/mhc/ops.py:178-188). */
 int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
-                    float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                    float* proj, float* sk_den, const void* x, const void* rmsnorm_weight, const void* phi,
                     const float* alpha, const float* bias, int64_t B, int n, int64_t C, int iters,
                     float eps, int dtype, void* workspace, size_t workspace_bytes,
                     mhc_stream_t stream);
@@ -105,13 +108,13 @@ int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_po
  * out:  dx [B,n,C] dtype;  fp32 parameter gradients, each written (not accumulated):
  *       d_rmsnorm_weight [C], d_phi [K, n*C], d_alpha [3], d_bias [K].  They may be slices of one
  *       flat bucket that is then all-reduced across data-parallel ranks.
- * in:   dy, x [B,n,C] dtype;  the forward's parameters and saved tensors. */
+ * in:   dy, x [B,n,C] dtype;  the forward's parameters and saved tensors (sk_den may be NULL). */
 int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha, float* d_bias,
                     const void* dy, const void* x, const void* rmsnorm_weight, const void* phi,
                     const float* alpha, const float* bias, const float* rms, const float* rms_h,
                     const float* H_pre, const float* H_post, const float* M, const float* proj,
-                    int64_t B, int n, int64_t C, int iters, float eps, int dtype, void* workspace,
-                    size_t workspace_bytes, mhc_stream_t stream);
+                    const float* sk_den, int64_t B, int n, int64_t C, int iters, float eps, int dtype,
+                    void* workspace, size_t workspace_bytes, mhc_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Static-H layer, forward: one set of coefficients shared by all tokens,

@@ -24,8 +24,8 @@ SIGNATURES = {
     "mhc_abi_version": (_i, []),
     "mhc_kernels_enqueued": (C.c_ulonglong, []),
     "mhc_workspace_bytes": (_z, [_i, _l, _i, _l, _i, _i]),
-    "mhc_dynamic_fwd": (_i, [_p] * 12 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
-    "mhc_dynamic_bwd": (_i, [_p] * 17 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_dynamic_fwd": (_i, [_p] * 13 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_dynamic_bwd": (_i, [_p] * 18 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_static_fwd": (_i, [_p] * 10 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_static_bwd": (_i, [_p] * 13 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_sinkhorn_fwd": (_i, [_p, _p, _l, _i, _i, _f, _p]),

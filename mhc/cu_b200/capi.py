@@ -57,7 +57,7 @@ def _workspace(nbytes: int, device, given=None):
 def dynamic_fwd(x, rmsnorm_weight, phi, alpha, bias, iters, eps, *, y=None, workspace=None):
     """mhc_dynamic_fwd.  x [B,n,C] fp32|bf16; rmsnorm_weight [C] bf16; phi [K,nC] same dtype as x
     (rows pre, post, res); alpha [3] fp32; bias [K] fp32.  Returns (y, saved) where saved holds the
-    fp32 tensors rms, rms_h, H_pre, H_post, M, proj."""
+    fp32 tensors rms, rms_h, H_pre, H_post, M, proj, sk_den."""
     B, n, C = x.shape
     K = 2 * n + n * n
     tag = _dtype_tag(x)
@@ -73,13 +73,15 @@ def dynamic_fwd(x, rmsnorm_weight, phi, alpha, bias, iters, eps, *, y=None, work
         "rms": torch.empty(B, **f32), "rms_h": torch.empty(B, **f32),
         "H_pre": torch.empty(B, n, **f32), "H_post": torch.empty(B, n, **f32),
         "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32),
+        "sk_den": torch.empty(B, 2 * int(iters), 4 if n <= 4 else 8, **f32),
     }
     nbytes = workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag)
     ws = _workspace(nbytes, dev, workspace)
     st = L.lib().mhc_dynamic_fwd(
         _ptr(y), _ptr(saved["rms"]), _ptr(saved["rms_h"]), _ptr(saved["H_pre"]), _ptr(saved["H_post"]),
-        _ptr(saved["M"]), _ptr(saved["proj"]), _ptr(x), _ptr(rmsnorm_weight), _ptr(phi), _ptr(alpha),
-        _ptr(bias), B, n, C, int(iters), float(eps), tag, _ptr(ws), ws.numel(), _stream())
+        _ptr(saved["M"]), _ptr(saved["proj"]), _ptr(saved["sk_den"]), _ptr(x), _ptr(rmsnorm_weight),
+        _ptr(phi), _ptr(alpha), _ptr(bias), B, n, C, int(iters), float(eps), tag, _ptr(ws),
+        ws.numel(), _stream())
     L.check(st, "mhc_dynamic_fwd")
     return y, saved
 
@@ -112,8 +114,8 @@ def dynamic_bwd(dy, x, rmsnorm_weight, phi, alpha, bias, saved, iters, eps, *, g
         _ptr(dx), _ptr(grads["d_rmsnorm_weight"]), _ptr(grads["d_phi"]), _ptr(grads["d_alpha"]),
         _ptr(grads["d_bias"]), _ptr(dy), _ptr(x), _ptr(rmsnorm_weight), _ptr(phi), _ptr(alpha),
         _ptr(bias), _ptr(saved["rms"]), _ptr(saved["rms_h"]), _ptr(saved["H_pre"]),
-        _ptr(saved["H_post"]), _ptr(saved["M"]), _ptr(saved["proj"]), B, n, C, int(iters), float(eps),
-        tag, _ptr(ws), ws.numel(), _stream())
+        _ptr(saved["H_post"]), _ptr(saved["M"]), _ptr(saved["proj"]), _ptr(saved.get("sk_den")),
+        B, n, C, int(iters), float(eps), tag, _ptr(ws), ws.numel(), _stream())
     L.check(st, "mhc_dynamic_bwd")
     return dx, grads
 

@@ -89,6 +89,7 @@ struct DynBwdWs {
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
         mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
         nblk = d.n <= 8 ? coeffs_thread_blocks(d) : coeffs_dyn_bwd_blocks(d);
+        const int nblk_max = nblk > coeffs_lanes_blocks(d) ? nblk : coeffs_lanes_blocks(d);
         fused = mma && bwd_fused_supported(d);
         ntb = fused ? bwd_fused_token_blocks(d) : (mma ? dx_mma_token_blocks(d) : dx_token_blocks(d));
         dphi_part = c.take<float>(fused && ntb > 1 ? (size_t)ntb * d.K() * d.nC() : 0);
@@ -100,7 +101,7 @@ struct DynBwdWs {
         c2 = c.take<float>((size_t)d.B);
         dpr = c.take<float>((size_t)d.B * d.K());
         qq = c.take<float>((size_t)d.B);
-        partials = c.take<float>((size_t)nblk * (d.K() + 3));
+        partials = c.take<float>((size_t)nblk_max * (d.K() + 3));
         dw_part = c.take<float>((size_t)ntb * d.C);
         const int G = group_lanes(d.n) < 2 ? 2 : group_lanes(d.n);
         const size_t per_token =
@@ -139,7 +140,7 @@ size_t sinkhorn_bwd_ws(int64_t batch, int n, int iters) {
 
 template <typename T>
 int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
-                  float* proj, const void* x, const void* w, const void* phi, const float* alpha,
+                  float* proj, float* sk_den, const void* x, const void* w, const void* phi, const float* alpha,
                   const float* bias, Dims d, int iters, float eps, int dtype, void* workspace,
                   cudaStream_t s) {
     Carver c(workspace);
@@ -155,7 +156,7 @@ int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post
     if (mix_fwd_supported(d, sizeof(T))) {
         MHC_TRY(launch_mix_fwd_dynamic<T>((T*)y, rms, rms_h, H_pre, H_post, M, proj, (const T*)x,
                                           (const bf16*)w, ws.praw, ws.sumsq, ws.nsplit, alpha, bias,
-                                          nullptr, d, iters, eps, dtype == MHC_F32, s));
+                                          sk_den, nullptr, d, iters, eps, dtype == MHC_F32, s));
         return MHC_OK;
     }
     MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, ws.nsplit, alpha,
@@ -169,8 +170,8 @@ template <typename T>
 int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_bias, const void* dy,
                   const void* x, const void* w, const void* phi, const float* alpha,
                   const float* bias, const float* rms, const float* rms_h, const float* H_pre,
-                  const float* H_post, const float* M, const float* proj, Dims d, int iters,
-                  float eps, int dtype, void* workspace, cudaStream_t s) {
+                  const float* H_post, const float* M, const float* proj, const float* sk_den,
+                  Dims d, int iters, float eps, int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     DynBwdWs ws(c, d, iters, dtype);
     if (bwd_reduce_staged_supported(d, sizeof(T)))
@@ -183,7 +184,13 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
     if (ws.mma) {
         mo.rec = ws.rec; mo.dprb = ws.dprb; mo.dprT = ws.dprT; mo.M = M; mo.rms = rms; mo.c2 = ws.c2;
     }
-    if (d.n <= 8)
+    // the forward leaves its Sinkhorn denominators only on the bf16 fused path
+    const bool lanes = sk_den != nullptr && dtype == MHC_BF16 && mix_fwd_supported(d, sizeof(T)) &&
+                       coeffs_lanes_supported(d, iters);
+    if (lanes)
+        MHC_TRY(launch_coeffs_dyn_bwd_lanes(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, M, proj,
+                                            rms_h, alpha, bias, sk_den, d, iters, mo, s));
+    else if (d.n <= 8)
         MHC_TRY(launch_coeffs_dyn_bwd_thread(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj,
                                              rms_h, alpha, bias, ws.den, d, iters, eps,
                                              dtype == MHC_F32, mo, s));
@@ -207,8 +214,8 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
                                  s));
         MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
     }
-    MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials, ws.nblk,
-                            d.n, s));
+    MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials,
+                            lanes ? coeffs_lanes_blocks(d) : ws.nblk, d.n, s));
     return MHC_OK;
 }
 
@@ -269,7 +276,7 @@ const char* mhc_status_string(int status) {
 
 const char* mhc_last_cuda_error(void) { return g_last_cuda_error; }
 
-int mhc_abi_version(void) { return 1; }
+int mhc_abi_version(void) { return 2; }
 
 unsigned long long mhc_kernels_enqueued(void) {
     return mhc::g_kernels_enqueued.load(std::memory_order_relaxed);
@@ -299,7 +306,7 @@ size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int d
 }
 
 int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
-                    float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                    float* proj, float* sk_den, const void* x, const void* rmsnorm_weight, const void* phi,
                     const float* alpha, const float* bias, int64_t B, int n, int64_t C, int iters,
                     float eps, int dtype, void* workspace, size_t workspace_bytes,
                     mhc_stream_t stream) {
@@ -316,18 +323,18 @@ int mhc_dynamic_fwd(void* y, float* rms, float* rms_h, float* H_pre, float* H_po
     const Dims d{B, n, C};
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (dtype == MHC_F32)
-        return dynamic_fwd_t<float>(y, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi,
-                                    alpha, bias, d, iters, eps, dtype, workspace, s);
-    return dynamic_fwd_t<bf16>(y, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi, alpha,
-                               bias, d, iters, eps, dtype, workspace, s);
+        return dynamic_fwd_t<float>(y, rms, rms_h, H_pre, H_post, M, proj, sk_den, x, rmsnorm_weight,
+                                    phi, alpha, bias, d, iters, eps, dtype, workspace, s);
+    return dynamic_fwd_t<bf16>(y, rms, rms_h, H_pre, H_post, M, proj, sk_den, x, rmsnorm_weight, phi,
+                               alpha, bias, d, iters, eps, dtype, workspace, s);
 }
 
 int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha, float* d_bias,
                     const void* dy, const void* x, const void* rmsnorm_weight, const void* phi,
                     const float* alpha, const float* bias, const float* rms, const float* rms_h,
                     const float* H_pre, const float* H_post, const float* M, const float* proj,
-                    int64_t B, int n, int64_t C, int iters, float eps, int dtype, void* workspace,
-                    size_t workspace_bytes, mhc_stream_t stream) {
+                    const float* sk_den, int64_t B, int n, int64_t C, int iters, float eps, int dtype,
+                    void* workspace, size_t workspace_bytes, mhc_stream_t stream) {
     if (int st = check_dims(B, n, C, iters, dtype)) return st;
     if (!d_rmsnorm_weight || !d_phi || !d_alpha || !d_bias || !rmsnorm_weight || !phi || !alpha ||
         !bias)
@@ -345,10 +352,10 @@ int mhc_dynamic_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_al
     if (dtype == MHC_F32)
         return dynamic_bwd_t<float>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, dy, x,
                                     rmsnorm_weight, phi, alpha, bias, rms, rms_h, H_pre, H_post, M,
-                                    proj, d, iters, eps, dtype, workspace, s);
+                                    proj, sk_den, d, iters, eps, dtype, workspace, s);
     return dynamic_bwd_t<bf16>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, dy, x, rmsnorm_weight,
-                               phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj, d, iters, eps,
-                               dtype, workspace, s);
+                               phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj, sk_den, d, iters,
+                               eps, dtype, workspace, s);
 }
 
 int mhc_static_fwd(void* y, float* rms, float* H_pre_act, float* H_post_act, float* M,

@@ -70,6 +70,14 @@ cudaError_t launch_coeffs_dyn_bwd_thread(float* dpr, float* qq, float* partials,
                                          const float* alpha, const float* bias, void* den_ws,
                                          Dims d, int iters, float eps, bool use_double,
                                          MmaBwdOut mma, cudaStream_t s);
+// n <= 4, float, with the forward's saved Sinkhorn denominators: sixteen lanes per token
+bool coeffs_lanes_supported(Dims d, int iters);
+int coeffs_lanes_blocks(Dims d);
+cudaError_t launch_coeffs_dyn_bwd_lanes(float* dpr, float* qq, float* partials, const float* dH,
+                                        const float* H_pre, const float* H_post, const float* M,
+                                        const float* proj, const float* rms_h, const float* alpha,
+                                        const float* bias, const float* sk_den, Dims d, int iters,
+                                        MmaBwdOut mma, cudaStream_t s);
 cudaError_t launch_coeffs_static_fwd(float* H_pre_act, float* H_post_act, float* M,
                                      const float* H_pre, const float* H_post, const float* H_res,
                                      int n, int iters, float eps, bool use_double, cudaStream_t s);
@@ -132,8 +140,9 @@ template <typename T>
 cudaError_t launch_mix_fwd_dynamic(T* y, float* rho, float* rms_h, float* H_pre, float* H_post,
                                    float* M, float* proj, const T* x, const bf16* w,
                                    const float* praw, const float* sumsq, int nsplit,
-                                   const float* alpha, const float* bias, int* status, Dims d,
-                                   int iters, float eps, bool use_double, cudaStream_t s);
+                                   const float* alpha, const float* bias, float* sk_den,
+                                   int* status, Dims d, int iters, float eps, bool use_double,
+                                   cudaStream_t s);
 template <typename T>
 cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
                                   const float* H_post, const float* M, int* status, Dims d,

@@ -16,6 +16,8 @@
 // rmsnorm_forward_with_rms and stream_distribute_mix_add_fused_dynamic of the reference
 // (src/csrc/include/utils.cuh:49-126, src/csrc/kernels/sinkhorn_knopp.cuh:827-1046,
 // src/csrc/kernels/stream_ops.cuh:451-642, src/csrc/kernels/rmsnorm.cuh:13-232).
+#include <type_traits>
+
 #include "async.cuh"
 #include "kernels.h"
 #include "sinkhorn.cuh"
@@ -50,6 +52,7 @@ struct MixFwdParams {
     const float* sumsq;  // [nsplit][B]
     const float* alpha;  // [3]
     const float* bias;   // [K]
+    float* sk_den;       // [B][2*iters][MAXN] out (float path only; may be NULL)
     int nsplit;
     int iters;
     int* status;         // device status word (may be NULL)
@@ -142,7 +145,15 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
 #pragma unroll
                 for (int j = 0; j < MAXN; ++j)
                     m[i][j] = (i < n && j < n) ? A(cfc[2 * MAXN + i * MAXN + j]) : A(0);
-            sk_forward_thread<MAXN, A, false>(m, n, p.iters, A(p.eps), nullptr);
+            if constexpr (std::is_same<A, float>::value) {
+                if (p.sk_den != nullptr)
+                    sk_forward_thread<MAXN, A, true>(m, n, p.iters, A(p.eps),
+                                                     p.sk_den + b * 2 * (int64_t)p.iters * MAXN);
+                else
+                    sk_forward_thread<MAXN, A, false>(m, n, p.iters, A(p.eps), nullptr);
+            } else {
+                sk_forward_thread<MAXN, A, false>(m, n, p.iters, A(p.eps), nullptr);
+            }
 #pragma unroll
             for (int i = 0; i < MAXN; ++i)
 #pragma unroll
@@ -299,15 +310,16 @@ template <typename T>
 cudaError_t launch_mix_fwd_dynamic(T* y, float* rho, float* rms_h, float* H_pre, float* H_post,
                                    float* M, float* proj, const T* x, const bf16* w,
                                    const float* praw, const float* sumsq, int nsplit,
-                                   const float* alpha, const float* bias, int* status, Dims d,
-                                   int iters, float eps, bool use_double, cudaStream_t s) {
+                                   const float* alpha, const float* bias, float* sk_den,
+                                   int* status, Dims d, int iters, float eps, bool use_double,
+                                   cudaStream_t s) {
     if (d.B == 0) return cudaSuccess;
     if (!mix_fwd_supported(d, sizeof(T))) return cudaErrorNotSupported;
     MixFwdParams<T> p{};
     p.y = y; p.rho = rho; p.x = x; p.w = w; p.H_pre = H_pre; p.H_post = H_post; p.M = M;
     p.proj = proj; p.rms_h = rms_h; p.praw = praw; p.sumsq = sumsq; p.alpha = alpha; p.bias = bias;
     p.nsplit = nsplit; p.iters = iters; p.status = status; p.B = d.B; p.C = d.C; p.n = d.n;
-    p.eps = eps;
+    p.eps = eps; p.sk_den = sk_den;
     return d.n <= 4 ? mix_fwd_launch<T, 4, true>(p, d, use_double, s)
                     : mix_fwd_launch<T, 8, true>(p, d, use_double, s);
 }
@@ -331,7 +343,8 @@ cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, c
     template cudaError_t launch_mix_fwd_dynamic<T>(T*, float*, float*, float*, float*, float*,     \
                                                    float*, const T*, const bf16*, const float*,    \
                                                    const float*, int, const float*, const float*,  \
-                                                   int*, Dims, int, float, bool, cudaStream_t);    \
+                                                   float*, int*, Dims, int, float, bool,           \
+                                                   cudaStream_t);                                  \
     template cudaError_t launch_mix_fwd_static<T>(T*, float*, const T*, const bf16*, const float*, \
                                                   const float*, const float*, int*, Dims, float,   \
                                                   cudaStream_t);

@@ -162,7 +162,7 @@ std::vector<Tensor> mhc_layer_bwd(Tensor dy, Tensor x, Tensor w, Tensor H_res, T
 
 // ---- dynamic-H layer -------------------------------------------------------------------------
 // phi [K, nC] in x's dtype (rows pre, post, res); alpha [3], bias [K] fp32 on the device.
-// returns (y, rms, rms_h, H_pre, H_post, M, proj)
+// returns (y, rms, rms_h, H_pre, H_post, M, proj, sk_den)
 std::vector<Tensor> mhc_layer_fwd_dynamic(Tensor x, Tensor w, Tensor phi, Tensor alpha, Tensor bias,
                                           int64_t iters, double eps) {
     need(x, "x_expanded"); need(w, "rmsnorm_weight"); need(phi, "phi"); need(alpha, "alpha");
@@ -177,20 +177,22 @@ std::vector<Tensor> mhc_layer_fwd_dynamic(Tensor x, Tensor w, Tensor phi, Tensor
     auto rms = torch::empty({B}, f32), rms_h = torch::empty({B}, f32);
     auto hp = torch::empty({B, n}, f32), hq = torch::empty({B, n}, f32);
     auto M = torch::empty({B, n, n}, f32), proj = torch::empty({B, K}, f32);
+    auto den = torch::empty({B, 2 * iters, n <= 4 ? 4 : 8}, f32);
     auto ws = workspace(MHC_OP_DYNAMIC_FWD, B, (int)n, C, (int)iters, tag, x);
     check(mhc_dynamic_fwd(y.data_ptr(), rms.data_ptr<float>(), rms_h.data_ptr<float>(),
                           hp.data_ptr<float>(), hq.data_ptr<float>(), M.data_ptr<float>(),
-                          proj.data_ptr<float>(), x.data_ptr(), w.data_ptr(), phi.data_ptr(),
-                          alpha.data_ptr<float>(), bias.data_ptr<float>(), B, (int)n, C, (int)iters,
-                          (float)eps, tag, ws.data_ptr(), ws.numel(), stream()),
+                          proj.data_ptr<float>(), den.data_ptr<float>(), x.data_ptr(), w.data_ptr(),
+                          phi.data_ptr(), alpha.data_ptr<float>(), bias.data_ptr<float>(), B, (int)n,
+                          C, (int)iters, (float)eps, tag, ws.data_ptr(), ws.numel(), stream()),
           "mhc_dynamic_fwd");
-    return {y, rms, rms_h, hp, hq, M, proj};
+    return {y, rms, rms_h, hp, hq, M, proj, den};
 }
 
 // returns (dx, d_rmsnorm_weight [C], d_phi [K,nC], d_alpha [3], d_bias [K]), gradients fp32
 std::vector<Tensor> mhc_layer_bwd_dynamic(Tensor dy, Tensor x, Tensor w, Tensor phi, Tensor alpha,
                                           Tensor bias, Tensor rms, Tensor rms_h, Tensor hp, Tensor hq,
-                                          Tensor M, Tensor proj, int64_t iters, double eps) {
+                                          Tensor M, Tensor proj, Tensor den, int64_t iters,
+                                          double eps) {
     need(dy, "grad_output"); need(x, "x_expanded");
     c10::cuda::CUDAGuard guard(x.device());
     const int64_t B = x.size(0), n = x.size(1), C = x.size(2), K = 2 * n + n * n;
@@ -205,8 +207,8 @@ std::vector<Tensor> mhc_layer_bwd_dynamic(Tensor dy, Tensor x, Tensor w, Tensor 
                           x.data_ptr(), w.data_ptr(), phi.data_ptr(), alpha.data_ptr<float>(),
                           bias.data_ptr<float>(), rms.data_ptr<float>(), rms_h.data_ptr<float>(),
                           hp.data_ptr<float>(), hq.data_ptr<float>(), M.data_ptr<float>(),
-                          proj.data_ptr<float>(), B, (int)n, C, (int)iters, (float)eps, tag,
-                          ws.data_ptr(), ws.numel(), stream()),
+                          proj.data_ptr<float>(), den.data_ptr<float>(), B, (int)n, C, (int)iters,
+                          (float)eps, tag, ws.data_ptr(), ws.numel(), stream()),
           "mhc_dynamic_bwd");
     return {dx, d_w, d_phi, d_alpha, d_bias};
 }

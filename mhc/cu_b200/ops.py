@@ -166,9 +166,9 @@ class MHCLayerDynamicFunction(Function):
         alpha = torch.stack([torch.as_tensor(a, dtype=torch.float32, device=dev).reshape(())
                              for a in (alpha_pre, alpha_post, alpha_res)]).float()
         bias = torch.cat([b_pre.reshape(-1), b_post.reshape(-1), b_res.reshape(-1)]).float()
-        y, rms, rms_h, hp, hq, M, proj = _ext().mhc_layer_fwd_dynamic(x, w, phi, alpha, bias,
-                                                                      sinkhorn_iters, eps)
-        ctx.save_for_backward(x, w, phi, alpha, bias, rms, rms_h, hp, hq, M, proj)
+        y, rms, rms_h, hp, hq, M, proj, den = _ext().mhc_layer_fwd_dynamic(
+            x, w, phi, alpha, bias, sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, phi, alpha, bias, rms, rms_h, hp, hq, M, proj, den)
         ctx.sinkhorn_iters = sinkhorn_iters
         ctx.eps = eps
         ctx.n = n
@@ -183,10 +183,10 @@ class MHCLayerDynamicFunction(Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj = ctx.saved_tensors
+        x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post, M, proj, den = ctx.saved_tensors
         dx, d_w, d_phi, d_alpha, d_bias = _ext().mhc_layer_bwd_dynamic(
             grad_output.contiguous().to(x.dtype), x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post,
-            M, proj, ctx.sinkhorn_iters, ctx.eps)
+            M, proj, den, ctx.sinkhorn_iters, ctx.eps)
         n = ctx.n
         dt = ctx.param_dtypes
         return (dx, d_w.to(dt[0]),

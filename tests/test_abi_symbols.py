@@ -52,7 +52,7 @@ def test_status_strings_and_workspace_sizes(lib):
 
 def test_validation_happens_before_any_cuda_call(lib):
     """Argument errors are reported without touching the device (works with no GPU present)."""
-    assert lib.mhc_dynamic_fwd(*([None] * 12), 4, 4, 64, 20, 1e-5, 0, None, 0, None) == 1
+    assert lib.mhc_dynamic_fwd(*([None] * 13), 4, 4, 64, 20, 1e-5, 0, None, 0, None) == 1
     assert lib.mhc_sinkhorn_fwd(None, None, 1, 40, 20, 1e-6, None) == 2
     assert lib.mhc_rmsnorm_fwd(None, None, None, None, 4, 0, 1e-5, None) == 2
 

@@ -75,7 +75,7 @@ def test_abi_rejects_bad_arguments():
     ws = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
     p = x.data_ptr()
     args = lambda n, dtype, ptr=p, wsb=ws.numel(): (
-        ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, 2, n, 64, 20, 1e-5, dtype,
+        ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, ptr, 2, n, 64, 20, 1e-5, dtype,
         ws.data_ptr(), wsb, None)
     assert h.mhc_dynamic_fwd(*args(0, 0)) == 2          # n out of range
     assert h.mhc_dynamic_fwd(*args(33, 0)) == 2
