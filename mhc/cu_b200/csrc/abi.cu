@@ -92,6 +92,7 @@ struct DynBwdWs {
         const int nblk_max = nblk > coeffs_lanes_blocks(d) ? nblk : coeffs_lanes_blocks(d);
         fused = mma && bwd_fused_supported(d);
         ntb = fused ? bwd_fused_token_blocks(d) : (mma ? dx_mma_token_blocks(d) : dx_token_blocks(d));
+        if (d.n > 8) ntb = (int)d.B;   // the wide dx pass leaves one d_weight row per token
         dphi_part = c.take<float>(fused && ntb > 1 ? (size_t)ntb * d.K() * d.nC() : 0);
         const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
         rec = c.take<float>(mma ? (size_t)d.B * bwd_mma_record_floats(d) : 0);
@@ -125,7 +126,7 @@ struct StaticBwdWs {
     void* den;
     int ntb;
     StaticBwdWs(Carver& c, Dims d, int iters, int dtype) {
-        ntb = dx_token_blocks(d);
+        ntb = d.n > 8 ? (int)d.B : dx_token_blocks(d);
         dH = c.take<float>((size_t)d.B * d.K());
         c2 = c.take<float>((size_t)d.B);
         dw_part = c.take<float>((size_t)ntb * d.C);
@@ -161,8 +162,12 @@ int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post
     }
     MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, ws.nsplit, alpha,
                                   bias, d, iters, eps, dtype == MHC_F32, s));
-    MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1, d,
-                                eps, s));
+    if (d.n > 8)
+        MHC_TRY(launch_apply_fwd_wide<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1,
+                                         d, eps, s));
+    else
+        MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, H_pre, H_post, M, 1, d,
+                                    eps, s));
     return MHC_OK;
 }
 
@@ -177,6 +182,9 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
     if (bwd_reduce_staged_supported(d, sizeof(T)))
         MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
                                             H_pre, H_post, 1, rms, nullptr, d, s));
+    else if (d.n > 8)
+        MHC_TRY(launch_bwd_reduce_wide<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
+                                          H_pre, H_post, 1, rms, d, s));
     else
         MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
                                      H_post, 1, rms, d, s));
@@ -209,13 +217,23 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
         }
     }
     if (!ws.mma) {
-        MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w,
-                                 H_pre, H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d,
-                                 s));
+        if (d.n > 8)
+            MHC_TRY(launch_bwd_dx_wide<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy,
+                                          (const bf16*)w, H_pre, H_post, M, 1, rms, ws.c2, ws.dpr,
+                                          ws.qq, (const T*)phi, d, s));
+        else
+            MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w,
+                                     H_pre, H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi,
+                                     d, s));
         MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
     }
+    DphiSum dsum;
+    if (ws.fused && ws.ntb > 1) {
+        dsum.dphi = d_phi; dsum.part = ws.dphi_part; dsum.nparts = ws.ntb;
+        dsum.total4 = (int64_t)d.K() * d.nC() / 4;
+    }
     MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials,
-                            lanes ? coeffs_lanes_blocks(d) : ws.nblk, d.n, s));
+                            lanes ? coeffs_lanes_blocks(d) : ws.nblk, d.n, s, dsum));
     return MHC_OK;
 }
 
@@ -230,7 +248,12 @@ int static_fwd_t(void* y, float* rms, float* hp, float* hq, float* M, const void
                                          d, eps, s));
         return MHC_OK;
     }
-    MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, 0, d, eps, s));
+    if (d.n > 8)
+        MHC_TRY(launch_apply_fwd_wide<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, 0, d,
+                                         eps, s));
+    else
+        MHC_TRY(launch_apply_fwd<T>((T*)y, rms, (const T*)x, (const bf16*)w, hp, hq, M, 0, d, eps,
+                                    s));
     return MHC_OK;
 }
 
@@ -244,13 +267,21 @@ int static_bwd_t(void* dx, float* d_w, float* d_H_pre, float* d_H_post, float* d
     if (bwd_reduce_staged_supported(d, sizeof(T)))
         MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
                                             hp, hq, 0, rms, nullptr, d, s));
+    else if (d.n > 8)
+        MHC_TRY(launch_bwd_reduce_wide<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, hp,
+                                          hq, 0, rms, d, s));
     else
         MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq,
                                      0, rms, d, s));
     MHC_TRY(launch_coeffs_static_bwd(d_H_pre, d_H_post, d_H_res, ws.dH, hp, hq, H_res, ws.den, d,
                                      iters, eps, dtype == MHC_F32, s));
-    MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, hp, hq,
-                             M, 0, rms, ws.c2, nullptr, nullptr, (const T*)nullptr, d, s));
+    if (d.n > 8)
+        MHC_TRY(launch_bwd_dx_wide<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w,
+                                      hp, hq, M, 0, rms, ws.c2, nullptr, nullptr, (const T*)nullptr,
+                                      d, s));
+    else
+        MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w, hp,
+                                 hq, M, 0, rms, ws.c2, nullptr, nullptr, (const T*)nullptr, d, s));
     MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, nullptr, nullptr, nullptr, 0, d.n, s));
     return MHC_OK;
 }

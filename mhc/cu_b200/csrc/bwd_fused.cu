@@ -14,7 +14,7 @@
 //   * dpr^T x x  on mma.sync as well: A = dpr^T (K x 16 tokens), B = the x tile read with
 //     ldmatrix.trans (token pairs packed), accumulators stay in registers across the token loop.
 // x and dy are read once; dx is written once; d_phi leaves as one partial per token range and is
-// added up in a fixed order by dphi_sum_kernel.
+// added up in a fixed order by the finalize launch.
 //
 // Takes over the eager GEMMs d_x_flat = d_p @ phi and d_phi = d_p^T @ x_flat of the reference's
 // dynamic backward (src/python/mhc/ops.py:330-349) and its stream_distribute_mix_backward /
@@ -358,19 +358,6 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
     }
 }
 
-// d_phi[i] = sum over token ranges of dphi_part[p][i], in order
-__global__ void dphi_sum_kernel(float* __restrict__ dphi, const float* __restrict__ part, int nparts,
-                                int64_t total4) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= total4) return;
-    float4 t = reinterpret_cast<const float4*>(part)[i];
-    for (int p = 1; p < nparts; ++p) {
-        const float4 v = reinterpret_cast<const float4*>(part)[(int64_t)p * total4 + i];
-        t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
-    }
-    reinterpret_cast<float4*>(dphi)[i] = t;
-}
-
 }  // namespace
 
 bool bwd_fused_supported(Dims d) { return d.n == 4 && d.C % 8 == 0 && d.nC() % 4 == 0; }
@@ -407,10 +394,6 @@ cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float*
     float* part = (ntb == 1) ? dphi : dphi_part;
     dx_dphi_kernel<4><<<grid, kFWarps * 32, smem, s>>>(dx, part, dw_part, x, g, w, rec, dprb, dprT,
                                                         phi, d.B, Bp, d.C, gpb);
-    cudaError_t e = launched();
-    if (e != cudaSuccess || ntb == 1) return e;
-    const int64_t total4 = (int64_t)d.K() * d.nC() / 4;
-    dphi_sum_kernel<<<(unsigned)((total4 + 255) / 256), 256, 0, s>>>(dphi, dphi_part, ntb, total4);
     return launched();
 }
 

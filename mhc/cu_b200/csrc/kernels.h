@@ -106,9 +106,16 @@ cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const b
                           const float* H_pre, const float* H_post, const float* M,
                           int coef_stride, const float* rms, const float* c2, const float* dpr,
                           const float* qq, const T* phi, Dims d, cudaStream_t s);
+// partial copies of d_phi left by the fused backward pass, to be added up by the finalize launch
+struct DphiSum {
+    float* dphi = nullptr;
+    const float* part = nullptr;
+    int nparts = 0;
+    int64_t total4 = 0;   // float4 items per copy; 0 = nothing to do
+};
 cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
                             float* d_alpha, const float* partials, int nparts2, int n,
-                            cudaStream_t s);
+                            cudaStream_t s, DphiSum ds = DphiSum());
 
 // ---- proj.cu: the two contractions against phi that reduce over columns / tokens --------------
 template <typename T>
@@ -158,10 +165,28 @@ cudaError_t launch_bwd_reduce_staged(float* dH, float* c2, const T* x, const T* 
 // ---- bwd_fused.cu: dx + partial d_phi + partial d_weight in one sweep over x and dy (bf16) -----
 bool bwd_fused_supported(Dims d);
 int bwd_fused_token_blocks(Dims d);   // rows of dw_part and partial copies of d_phi [K][nC]
+// With more than one token range the result is left in dphi_part (bwd_fused_token_blocks copies)
+// for launch_finalize to add up; with one range it is written to dphi directly.
 cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float* dw_part,
                                  const bf16* x, const bf16* g, const bf16* w, const float* rec,
                                  const bf16* dprb, const bf16* dprT, const bf16* phi, Dims d,
                                  cudaStream_t s);
+
+// ---- wide_ops.cu: the stream passes for 8 < n <= 32 (coefficients in shared memory) -----------
+template <typename T>
+cudaError_t launch_apply_fwd_wide(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                                  const float* H_post, const float* M, int coef_stride, Dims d,
+                                  float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_bwd_reduce_wide(float* dH, float* c2, const T* x, const T* g, const bf16* w,
+                                   const float* H_pre, const float* H_post, int coef_stride,
+                                   const float* rms, Dims d, cudaStream_t s);
+// writes one d_weight row per token: dw_part is [B][C]
+template <typename T>
+cudaError_t launch_bwd_dx_wide(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
+                               const float* H_pre, const float* H_post, const float* M,
+                               int coef_stride, const float* rms, const float* c2, const float* dpr,
+                               const float* qq, const T* phi, Dims d, cudaStream_t s);
 
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,

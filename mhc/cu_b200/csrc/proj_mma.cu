@@ -48,7 +48,7 @@ __device__ __forceinline__ float sumsq8(const uint4& v) {
 // CH = chunks of 32 reduction elements per warp (compile-time so that all loads of x are issued
 // before the first MMA).
 template <int NT, int CH>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, (NT * CH <= 15) ? 2 : 1)
 proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
                 const bf16* __restrict__ x, const bf16* __restrict__ phi, int64_t B, int K,
                 int64_t nC) {
@@ -91,14 +91,23 @@ proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
         prow[t] = phi + (int64_t)(pval[t] ? row : 0) * nC;
     }
 
-    float sslo = 0.f, sshi = 0.f;
+    // all phi fragments of this warp's slice are requested before the first MMA, so x (HBM) and
+    // phi (L2) arrive within one round trip instead of one per chunk
+    uint4 pf[CH][NT];
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
         const int64_t k = kbeg + (int64_t)c * kChunk + 8 * q;
         const bool in = k < nC;
 #pragma unroll
+        for (int t = 0; t < NT; ++t)
+            pf[c][t] = (in && pval[t]) ? *reinterpret_cast<const uint4*>(prow[t] + k) : zero;
+    }
+    float sslo = 0.f, sshi = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+#pragma unroll
         for (int t = 0; t < NT; ++t) {
-            const uint4 p = (in && pval[t]) ? *reinterpret_cast<const uint4*>(prow[t] + k) : zero;
+            const uint4 p = pf[c][t];
             mma_bf16_16816(acc[t], r[c].x, s[c].x, r[c].y, s[c].y, p.x, p.y);
             mma_bf16_16816(acc[t], r[c].z, s[c].z, r[c].w, s[c].w, p.z, p.w);
         }

@@ -340,24 +340,40 @@ bwd_dx_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restri
     }
 }
 
-// d_w[c] = sum_parts dw_part[p][c];  d_bias[k], d_alpha[0..2] = sums of partials[p][K+3].
+// One launch for every fixed-order sum over partial results of the backward:
+//   d_w[c] = sum_p dw_part[p][c];  d_bias[k], d_alpha[0..2] = sum_p partials[p][K+3];
+//   d_phi[i] = sum_p dphi_part[p][i]  (float4 items; only when the fused pass left partial copies).
 __global__ void finalize_kernel(float* __restrict__ d_w, const float* __restrict__ dw_part,
                                 int nparts, int64_t C, float* __restrict__ d_bias,
                                 float* __restrict__ d_alpha, const float* __restrict__ partials,
-                                int nparts2, int K) {
+                                int nparts2, int K, DphiSum ds) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < ds.total4) {
+        float4 t = reinterpret_cast<const float4*>(ds.part)[i];
+        for (int p = 1; p < ds.nparts; ++p) {
+            const float4 v = reinterpret_cast<const float4*>(ds.part)[(int64_t)p * ds.total4 + i];
+            t.x += v.x; t.y += v.y; t.z += v.z; t.w += v.w;
+        }
+        reinterpret_cast<float4*>(ds.dphi)[i] = t;
+    }
     if (i < C) {
         float t = 0.f;
         for (int p = 0; p < nparts; ++p) t += dw_part[(int64_t)p * C + i];
         d_w[i] = t;
     }
-    if (d_bias != nullptr && i < K + 3) {
+    // d_bias / d_alpha: one warp per output, lanes stride over the partial rows, then a butterfly
+    // (the order of additions is fixed by the layout, not by timing)
+    if (d_bias != nullptr && i < (int64_t)(K + 3) * 32) {
+        const int k = (int)(i >> 5), lane = (int)(i & 31);
         float t = 0.f;
-        for (int p = 0; p < nparts2; ++p) t += partials[(int64_t)p * (K + 3) + i];
-        if (i < K)
-            d_bias[i] = t;
-        else
-            d_alpha[i - K] = t;
+        for (int p = lane; p < nparts2; p += 32) t += partials[(int64_t)p * (K + 3) + k];
+        t = warp_sum(t);
+        if (lane == 0) {
+            if (k < K)
+                d_bias[k] = t;
+            else
+                d_alpha[k - K] = t;
+        }
     }
 }
 
@@ -470,12 +486,13 @@ cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const b
 
 cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
                             float* d_alpha, const float* partials, int nparts2, int n,
-                            cudaStream_t s) {
+                            cudaStream_t s, DphiSum ds) {
     const int K = 2 * n + n * n;
-    int64_t items = C > K + 3 ? C : K + 3;
+    int64_t items = C > (int64_t)(K + 3) * 32 ? C : (int64_t)(K + 3) * 32;
+    if (ds.total4 > items) items = ds.total4;
     const unsigned grid = (unsigned)((items + 255) / 256);
     finalize_kernel<<<grid, 256, 0, s>>>(d_w, dw_part, nparts, C, d_bias, d_alpha, partials, nparts2,
-                                         K);
+                                         K, ds);
     return launched();
 }
 

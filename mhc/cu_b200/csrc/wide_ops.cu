@@ -1,0 +1,318 @@
+// Stream passes for wide expansion rates (8 < n <= 32): the per-token coefficient matrix no longer
+// fits in registers, so it sits in shared memory and every thread keeps one column of all n streams
+// in registers instead.  Same math and same outputs as stream_ops.cu; any C, fp32 or bf16.
+// These are the general-purpose kernels for n = 9..32 (correctness first; the n <= 8 family has the
+// tuned kernels).
+//
+// Takes over, for n up to 32, what the reference does with its MAX_N-templated stream kernels
+// (src/csrc/kernels/stream_ops.cuh:332-449,528-642,956-997).
+#include "kernels.h"
+
+namespace mhc {
+
+namespace {
+
+constexpr int kWideThreads = 256;
+constexpr int kWMax = kMaxStreams;   // 32
+
+template <typename T>
+__device__ __forceinline__ float ldf(const T* p);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void stf(T* p, float v);
+template <>
+__device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void stf<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float block_total(float v, float* scratch) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += scratch[w];
+    return t;
+}
+
+// ---- forward: one block per token --------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads)
+apply_fwd_wide_kernel(T* __restrict__ y, float* __restrict__ rho_out, const T* __restrict__ x,
+                      const bf16* __restrict__ w, const float* __restrict__ H_pre,
+                      const float* __restrict__ H_post, const float* __restrict__ M,
+                      int coef_stride, int n, int64_t C, float eps) {
+    extern __shared__ float sm[];   // hp[n] hq[n] m[n*n] scratch[32]
+    float* hp = sm;
+    float* hq = hp + n;
+    float* m = hq + n;
+    float* scratch = m + n * n;
+    const int64_t b = blockIdx.x;
+    const int64_t cb = b * coef_stride;
+    for (int k = threadIdx.x; k < n; k += kWideThreads) {
+        hp[k] = H_pre[cb * n + k];
+        hq[k] = H_post[cb * n + k];
+    }
+    for (int k = threadIdx.x; k < n * n; k += kWideThreads) m[k] = M[cb * n * n + k];
+    __syncthreads();
+    const T* xb = x + b * n * C;
+    T* yb = y + b * n * C;
+    float ss = 0.f;
+    for (int64_t c = threadIdx.x; c < C; c += kWideThreads) {
+        float a = 0.f;
+        for (int i = 0; i < n; ++i) a = fmaf(hp[i], ldf<T>(xb + i * C + c), a);
+        ss = fmaf(a, a, ss);
+    }
+    const float tot = block_total(ss, scratch);
+    const float rho = sqrtf(tot / (float)C + eps);
+    const float ri = 1.f / rho;
+    if (threadIdx.x == 0) rho_out[b] = rho;
+    for (int64_t c = threadIdx.x; c < C; c += kWideThreads) {
+        float xc[kWMax];
+        float a = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWMax; ++i) {
+            xc[i] = (i < n) ? ldf<T>(xb + i * C + c) : 0.f;
+            if (i < n) a = fmaf(hp[i], xc[i], a);
+        }
+        const float yn = a * ri * __bfloat162float(w[c]);
+        for (int i = 0; i < n; ++i) {
+            float t = hq[i] * yn;
+#pragma unroll
+            for (int j = 0; j < kWMax; ++j)
+                if (j < n) t = fmaf(m[i * n + j], xc[j], t);
+            stf<T>(yb + i * C + c, t);
+        }
+    }
+}
+
+// ---- backward pass A: per-token inner products, one block per token --------------------------
+// Columns are staged in chunks in shared memory; thread pairs (i,j) own the dM entries.
+constexpr int kWChunk = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(kWideThreads)
+bwd_reduce_wide_kernel(float* __restrict__ dH, float* __restrict__ c2_out,
+                       const T* __restrict__ x, const T* __restrict__ g,
+                       const bf16* __restrict__ w, const float* __restrict__ H_pre,
+                       const float* __restrict__ H_post, int coef_stride,
+                       const float* __restrict__ rms, int n, int64_t C) {
+    extern __shared__ float sm[];
+    // xs[n][CH+1] gs[n][CH+1] a[CH] u[CH] aw[CH] hp[n] hq[n] scratch[32]
+    constexpr int CH = kWChunk, LD = kWChunk + 1;
+    float* xs = sm;
+    float* gs = xs + n * LD;
+    float* as = gs + n * LD;
+    float* us = as + CH;
+    float* aws = us + CH;
+    float* hp = aws + CH;
+    float* hq = hp + n;
+    float* scratch = hq + n;
+    const int64_t b = blockIdx.x;
+    const int64_t cb = b * coef_stride;
+    for (int k = threadIdx.x; k < n; k += kWideThreads) {
+        hp[k] = H_pre[cb * n + k];
+        hq[k] = H_post[cb * n + k];
+    }
+    const T* xb = x + b * n * C;
+    const T* gb = g + b * n * C;
+    const int K = 2 * n + n * n;
+    // outputs owned by this thread: indices o = tid, tid + 256, ... over
+    //   [0, n*n): dM[i][j]   [n*n, +n): P   [.., +n): ux   [.., +n): ax   last: s
+    const int NO = n * n + 3 * n + 1;
+    constexpr int OPT = (kWMax * kWMax + 3 * kWMax + 1 + kWideThreads - 1) / kWideThreads;   // 5
+    float acc[OPT];
+#pragma unroll
+    for (int u = 0; u < OPT; ++u) acc[u] = 0.f;
+
+    for (int64_t c0 = 0; c0 < C; c0 += CH) {
+        const int cn = (C - c0 < CH) ? (int)(C - c0) : CH;
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * CH; e += kWideThreads) {
+            const int i = e / CH, c = e % CH;
+            const bool in = c < cn;
+            xs[i * LD + c] = in ? ldf<T>(xb + i * C + c0 + c) : 0.f;
+            gs[i * LD + c] = in ? ldf<T>(gb + i * C + c0 + c) : 0.f;
+        }
+        __syncthreads();
+        for (int c = threadIdx.x; c < CH; c += kWideThreads) {
+            float a = 0.f, dyh = 0.f;
+            for (int i = 0; i < n; ++i) {
+                a = fmaf(hp[i], xs[i * LD + c], a);
+                dyh = fmaf(hq[i], gs[i * LD + c], dyh);
+            }
+            const float wc = (c < cn) ? __bfloat162float(w[c0 + c]) : 0.f;
+            as[c] = a;
+            us[c] = dyh * wc;
+            aws[c] = a * wc;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < OPT; ++u) {
+            const int o = threadIdx.x + u * kWideThreads;
+            if (o >= NO) continue;
+            float t = 0.f;
+            if (o < n * n) {
+                const float* gi = gs + (o / n) * LD;
+                const float* xj = xs + (o % n) * LD;
+                for (int c = 0; c < CH; ++c) t = fmaf(gi[c], xj[c], t);
+            } else if (o < n * n + n) {
+                const float* gi = gs + (o - n * n) * LD;
+                for (int c = 0; c < CH; ++c) t = fmaf(gi[c], aws[c], t);
+            } else if (o < n * n + 2 * n) {
+                const float* xi = xs + (o - n * n - n) * LD;
+                for (int c = 0; c < CH; ++c) t = fmaf(us[c], xi[c], t);
+            } else if (o < n * n + 3 * n) {
+                const float* xi = xs + (o - n * n - 2 * n) * LD;
+                for (int c = 0; c < CH; ++c) t = fmaf(as[c], xi[c], t);
+            } else {
+                for (int c = 0; c < CH; ++c) t = fmaf(us[c], as[c], t);
+            }
+            acc[u] += t;
+        }
+    }
+    // publish the totals through shared memory (reuse xs), then finish
+    __syncthreads();
+    float* tot = xs;
+#pragma unroll
+    for (int u = 0; u < OPT; ++u) {
+        const int o = threadIdx.x + u * kWideThreads;
+        if (o < NO) tot[o] = acc[u];
+    }
+    __syncthreads();
+    const float ri = 1.f / rms[b];
+    const float c2 = tot[n * n + 3 * n] * ri * ri * ri / (float)C;
+    if (threadIdx.x == 0) c2_out[b] = c2;
+    (void)scratch;
+    for (int k = threadIdx.x; k < K; k += kWideThreads) {
+        float o;
+        if (k < n)
+            o = ri * tot[n * n + n + k] - c2 * tot[n * n + 2 * n + k];
+        else if (k < 2 * n)
+            o = tot[n * n + (k - n)] * ri;
+        else
+            o = tot[k - 2 * n];
+        dH[b * K + k] = o;
+    }
+}
+
+// ---- backward pass B: dx and the per-token d_weight row, one block per token -------------------
+template <typename T, bool DYNAMIC>
+__global__ void __launch_bounds__(kWideThreads)
+bwd_dx_wide_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restrict__ x,
+                   const T* __restrict__ g, const bf16* __restrict__ w,
+                   const float* __restrict__ H_pre, const float* __restrict__ H_post,
+                   const float* __restrict__ M, int coef_stride, const float* __restrict__ rms,
+                   const float* __restrict__ c2, const float* __restrict__ dpr,
+                   const float* __restrict__ qq, const T* __restrict__ phi, int n, int64_t C) {
+    extern __shared__ float sm[];   // hp[n] hq[n] m[n*n] dp[K]
+    const int K = 2 * n + n * n;
+    float* hp = sm;
+    float* hq = hp + n;
+    float* m = hq + n;
+    float* dp = m + n * n;
+    const int64_t b = blockIdx.x;
+    const int64_t cb = b * coef_stride;
+    for (int k = threadIdx.x; k < n; k += kWideThreads) {
+        hp[k] = H_pre[cb * n + k];
+        hq[k] = H_post[cb * n + k];
+    }
+    for (int k = threadIdx.x; k < n * n; k += kWideThreads) m[k] = M[cb * n * n + k];
+    if (DYNAMIC)
+        for (int k = threadIdx.x; k < K; k += kWideThreads) dp[k] = dpr[b * K + k];
+    __syncthreads();
+    const float ri = 1.f / rms[b];
+    const float c2b = c2[b];
+    const float qb = DYNAMIC ? qq[b] : 0.f;
+    const int64_t nC = (int64_t)n * C;
+    const T* xb = x + b * nC;
+    const T* gb = g + b * nC;
+    for (int64_t c = threadIdx.x; c < C; c += kWideThreads) {
+        float xc[kWMax], gc[kWMax];
+        float a = 0.f, dyh = 0.f;
+#pragma unroll
+        for (int i = 0; i < kWMax; ++i) {
+            xc[i] = (i < n) ? ldf<T>(xb + i * C + c) : 0.f;
+            gc[i] = (i < n) ? ldf<T>(gb + i * C + c) : 0.f;
+            a = fmaf(hp[i < n ? i : 0], xc[i], a);
+            dyh = fmaf(hq[i < n ? i : 0], gc[i], dyh);
+        }
+        const float wc = __bfloat162float(w[c]);
+        const float da = dyh * wc * ri - a * c2b;
+        dw_part[b * C + c] = dyh * ri * a;
+        for (int j = 0; j < n; ++j) {
+            float t = fmaf(hp[j], da, -qb * xc[j]);
+#pragma unroll
+            for (int i = 0; i < kWMax; ++i)
+                if (i < n) t = fmaf(m[i * n + j], gc[i], t);
+            if (DYNAMIC) {
+                const T* ph = phi + (int64_t)j * C + c;
+                for (int k = 0; k < K; ++k) t = fmaf(dp[k], ldf<T>(ph + (int64_t)k * nC), t);
+            }
+            stf<T>(dx + b * nC + j * C + c, t);
+        }
+    }
+}
+
+}  // namespace
+
+template <typename T>
+cudaError_t launch_apply_fwd_wide(T* y, float* rho, const T* x, const bf16* w, const float* H_pre,
+                                  const float* H_post, const float* M, int coef_stride, Dims d,
+                                  float eps, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    const size_t smem = (size_t)(2 * d.n + d.n * d.n + 32) * sizeof(float);
+    apply_fwd_wide_kernel<T><<<(unsigned)d.B, kWideThreads, smem, s>>>(y, rho, x, w, H_pre, H_post, M,
+                                                                       coef_stride, d.n, d.C, eps);
+    return launched();
+}
+
+template <typename T>
+cudaError_t launch_bwd_reduce_wide(float* dH, float* c2, const T* x, const T* g, const bf16* w,
+                                   const float* H_pre, const float* H_post, int coef_stride,
+                                   const float* rms, Dims d, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    size_t fl = (size_t)2 * d.n * (kWChunk + 1) + 3 * kWChunk + 2 * d.n + 32;
+    const size_t need_tot = (size_t)d.n * d.n + 3 * d.n + 1;   // totals reuse the xs area
+    if ((size_t)d.n * (kWChunk + 1) < need_tot) fl += need_tot;
+    bwd_reduce_wide_kernel<T><<<(unsigned)d.B, kWideThreads, fl * sizeof(float), s>>>(
+        dH, c2, x, g, w, H_pre, H_post, coef_stride, rms, d.n, d.C);
+    return launched();
+}
+
+// dw_part gets one row per token: rows = B
+template <typename T>
+cudaError_t launch_bwd_dx_wide(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
+                               const float* H_pre, const float* H_post, const float* M,
+                               int coef_stride, const float* rms, const float* c2, const float* dpr,
+                               const float* qq, const T* phi, Dims d, cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    const size_t smem = (size_t)(2 * d.n + d.n * d.n + d.K()) * sizeof(float);
+    if (phi != nullptr)
+        bwd_dx_wide_kernel<T, true><<<(unsigned)d.B, kWideThreads, smem, s>>>(
+            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, d.n, d.C);
+    else
+        bwd_dx_wide_kernel<T, false><<<(unsigned)d.B, kWideThreads, smem, s>>>(
+            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, d.n, d.C);
+    return launched();
+}
+
+#define MHC_INST(T)                                                                                \
+    template cudaError_t launch_apply_fwd_wide<T>(T*, float*, const T*, const bf16*, const float*, \
+                                                  const float*, const float*, int, Dims, float,    \
+                                                  cudaStream_t);                                   \
+    template cudaError_t launch_bwd_reduce_wide<T>(float*, float*, const T*, const T*, const bf16*, \
+                                                   const float*, const float*, int, const float*,  \
+                                                   Dims, cudaStream_t);                            \
+    template cudaError_t launch_bwd_dx_wide<T>(T*, float*, const T*, const T*, const bf16*,        \
+                                               const float*, const float*, const float*, int,      \
+                                               const float*, const float*, const float*,           \
+                                               const float*, const T*, Dims, cudaStream_t);
+MHC_INST(float)
+MHC_INST(bf16)
+#undef MHC_INST
+
+}  // namespace mhc

@@ -14,7 +14,7 @@ class MHCLayer(nn.Module):
 
     Args:
         hidden_dim: C.
-        expansion_rate: n, the number of residual streams (1..32; kernels exist for n <= 8).
+        expansion_rate: n, the number of residual streams (1..32; tuned kernels for n <= 8).
         sinkhorn_iters: Sinkhorn-Knopp iterations.
         eps: the one epsilon shared by both RMS norms and by Sinkhorn.
         alpha_init: initial value of the three alpha scalars (and scale of the static H_res).

@@ -108,7 +108,7 @@ def test_training_steps_and_batch_sizes(dynamic):
         loss = ((layer(x) - target) ** 2).mean()
         loss.backward()
         opt.step()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     assert all(l == l for l in losses) and losses[-1] < losses[0]
     for B in (1, 4, 16, 32):
         assert layer(torch.randn(B, 4, 128, device="cuda")).shape == (B, 4, 128)
@@ -156,6 +156,22 @@ def test_state_dict_round_trip():
     b.load_state_dict(a.state_dict())
     x = torch.randn(4, 4, 64, device="cuda")
     assert torch.equal(a(x), b(x))
+
+
+@pytest.mark.parametrize("n", [8, 32])
+def test_other_expansion_rates_through_the_layer(n):
+    """n = 8 and n = 32 as in the reference's benchmark table (README.md:86-104 of the reference)."""
+    layer = _layer(64, n, True)
+    x = torch.randn(6, n, 64, device="cuda", requires_grad=True)
+    dy = torch.randn(6, n, 64, device="cuda")
+    y = layer(x)
+    y.backward(dy)
+    params = {k: v.detach().cpu() for k, v in layer.named_parameters()}
+    ref = oracle.dynamic_fwd_bwd(x.detach().cpu(), params, dy.cpu(), layer.sinkhorn_iters, layer.eps,
+                                 dtype=torch.float64)
+    assert_rel(y, ref["y"], 1e-5, "y")
+    assert_rel(x.grad, ref["dx"], 1e-5, "dx")
+    assert_rel(layer.phi_res.grad, ref["dphi_res"], 1e-5, "dphi_res")
 
 
 def test_default_is_dynamic():

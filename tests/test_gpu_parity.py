@@ -34,7 +34,7 @@ def _check(out, ref, keys, tol, scales=None):
 
 
 def _golden_small(prefix):
-    return [n for n in golden_names(prefix) if int(n.split("_n")[1].split("_")[0]) <= 8]
+    return golden_names(prefix)
 
 
 @pytest.mark.parametrize("name", _golden_small("dyn"))
@@ -68,6 +68,10 @@ DYN_SHAPES = [
     (7, 4, 100, 0.5, 0.3),   # C not a multiple of the 16-byte vector for bf16
     (3, 4, 6, 0.5, 0.3),     # nor for fp32
     (40, 4, 4104, 0.3, 0.1),  # more column vectors than one block caches
+    (4, 12, 40, 0.4, 0.2),    # wide expansion rates: coefficients in shared memory
+    (3, 16, 24, 0.4, 0.2),
+    (2, 32, 16, 0.3, 0.1),
+    (5, 32, 72, 0.3, 0.1),
 ]
 
 
@@ -84,7 +88,7 @@ def test_dynamic_seeded(B, n, C, alpha, bs, dtype):
 
 
 STATIC_SHAPES = [(1, 4, 16), (8, 4, 128), (32, 4, 128), (17, 4, 136), (320, 4, 1280), (6, 8, 64),
-                 (5, 3, 40), (7, 4, 100), (3, 4, 6)]
+                 (5, 3, 40), (7, 4, 100), (3, 4, 6), (4, 16, 32), (3, 32, 24), (32, 32, 128)]
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=_ids.get)
@@ -109,7 +113,8 @@ def test_dynamic_full_size(cfg):
     out, saved = run_dynamic(x, dy, params, c["iters"], c["eps"], dtype)
     xo, dyo, po = oracle_inputs(x, dy, params, dtype)
     ref = oracle.dynamic_fwd_bwd(xo, po, dyo, c["iters"], c["eps"], dtype=torch.float64)
-    _check(out, ref, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], TOL[dtype])
+    scales = oracle.dynamic_backward_closed_form(xo, po, dyo, c["iters"], c["eps"])
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], TOL[dtype], scales)
     M = saved["M"].double().cpu()
     assert float((M.sum(-1) - 1).abs().max()) <= 1e-5
     assert float((M.sum(-2) - 1).abs().max()) <= 1e-5
@@ -120,6 +125,22 @@ def test_dynamic_full_size(cfg):
     out2, _ = run_dynamic(x[sub], dy[sub], params, c["iters"], c["eps"], dtype)
     assert_rel(out2["y"], out["y"][sub], 1e-2, "y of a sub-batch")
     assert_rel(out2["dx"], out["dx"][sub], 1e-2, "dx of a sub-batch")
+
+
+def test_dynamic_full_size_c4_wide():
+    """Wide expansion (n = 32, B = 128, C = 1280, bf16): parity with the fp64 oracle."""
+    c = synthetic.CONFIGS["c4"]
+    B, n, C, dtype = c["B"], c["n"], c["C"], c["dtype"]
+    params = synthetic.dynamic_params(n, C, seed=0)
+    x, dy = synthetic.streams(B, n, C, seed=0)
+    out, saved = run_dynamic(x, dy, params, c["iters"], c["eps"], dtype)
+    xo, dyo, po = oracle_inputs(x, dy, params, dtype)
+    ref = oracle.dynamic_fwd_bwd(xo, po, dyo, c["iters"], c["eps"], dtype=torch.float64)
+    scales = oracle.dynamic_backward_closed_form(xo, po, dyo, c["iters"], c["eps"])
+    _check(out, ref, ["y", "dx"] + ["d" + k for k in DYN_PARAMS], TOL[dtype], scales)
+    M = saved["M"].double().cpu()
+    assert float((M.sum(-1) - 1).abs().max()) <= 1e-4
+    assert float((M.sum(-2) - 1).abs().max()) <= 1e-4
 
 
 def test_static_full_size_c1():
