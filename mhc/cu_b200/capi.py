@@ -46,12 +46,29 @@ def workspace_bytes(op: int, B: int, n: int, C: int, iters: int, dtype_tag: int)
     return v
 
 
+# Debug aid for the parity tests: when set, every buffer this module allocates (outputs, saved
+# tensors, workspace) starts as all-ones bytes (NaN in every floating type), so a kernel that reads
+# a slot nobody wrote shows up in the results instead of depending on what the allocator returns.
+POISON = False
+
+
+def _empty(*shape, **kw):
+    t = torch.empty(*shape, **kw)
+    if POISON and t.numel():
+        t.view(torch.uint8).fill_(0xFF)
+    return t
+
+
+def _empty_like(t):
+    return _empty(t.shape, dtype=t.dtype, device=t.device)
+
+
 def _workspace(nbytes: int, device, given=None):
     if given is not None:
         if given.numel() * given.element_size() < nbytes:
             raise ValueError("workspace too small")
         return given
-    return torch.empty(max(nbytes, 16), dtype=torch.uint8, device=device)
+    return _empty(max(nbytes, 16), dtype=torch.uint8, device=device)
 
 
 def dynamic_fwd(x, rmsnorm_weight, phi, alpha, bias, iters, eps, *, y=None, workspace=None):
@@ -68,12 +85,12 @@ def dynamic_fwd(x, rmsnorm_weight, phi, alpha, bias, iters, eps, *, y=None, work
     _chk(bias, "bias", torch.float32, (K,))
     dev = x.device
     f32 = dict(dtype=torch.float32, device=dev)
-    y = torch.empty_like(x) if y is None else _chk(y, "y", x.dtype, x.shape)
+    y = _empty_like(x) if y is None else _chk(y, "y", x.dtype, x.shape)
     saved = {
-        "rms": torch.empty(B, **f32), "rms_h": torch.empty(B, **f32),
-        "H_pre": torch.empty(B, n, **f32), "H_post": torch.empty(B, n, **f32),
-        "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32),
-        "sk_den": torch.empty(B, 2 * int(iters), 4 if n <= 4 else 8, **f32),
+        "rms": _empty(B, **f32), "rms_h": _empty(B, **f32),
+        "H_pre": _empty(B, n, **f32), "H_post": _empty(B, n, **f32),
+        "M": _empty(B, n, n, **f32), "proj": _empty(B, K, **f32),
+        "sk_den": _empty(B, 2 * int(iters), 4 if n <= 4 else 8, **f32),
     }
     nbytes = workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag)
     ws = _workspace(nbytes, dev, workspace)
@@ -101,13 +118,13 @@ def dynamic_bwd(dy, x, rmsnorm_weight, phi, alpha, bias, saved, iters, eps, *, g
     dev = x.device
     f32 = dict(dtype=torch.float32, device=dev)
     if grads is None:
-        grads = {"d_rmsnorm_weight": torch.empty(C, **f32), "d_phi": torch.empty(K, n * C, **f32),
-                 "d_alpha": torch.empty(3, **f32), "d_bias": torch.empty(K, **f32)}
+        grads = {"d_rmsnorm_weight": _empty(C, **f32), "d_phi": _empty(K, n * C, **f32),
+                 "d_alpha": _empty(3, **f32), "d_bias": _empty(K, **f32)}
     _chk(grads["d_rmsnorm_weight"], "d_rmsnorm_weight", torch.float32, (C,))
     _chk(grads["d_phi"], "d_phi", torch.float32, (K, n * C))
     _chk(grads["d_alpha"], "d_alpha", torch.float32, (3,))
     _chk(grads["d_bias"], "d_bias", torch.float32, (K,))
-    dx = torch.empty_like(x) if dx is None else _chk(dx, "dx", x.dtype, x.shape)
+    dx = _empty_like(x) if dx is None else _chk(dx, "dx", x.dtype, x.shape)
     nbytes = workspace_bytes(L.OP_DYNAMIC_BWD, B, n, C, iters, tag)
     ws = _workspace(nbytes, dev, workspace)
     st = L.lib().mhc_dynamic_bwd(
@@ -134,11 +151,11 @@ def static_fwd(x, rmsnorm_weight, H_pre, H_post, H_res, iters, eps, *, inference
     _chk(H_res, "H_res", torch.float32, (n, n))
     dev = x.device
     f32 = dict(dtype=torch.float32, device=dev)
-    y = torch.empty_like(x) if y is None else _chk(y, "y", x.dtype, x.shape)
+    y = _empty_like(x) if y is None else _chk(y, "y", x.dtype, x.shape)
     saved = None
     if not inference:
-        saved = {"rms": torch.empty(B, **f32), "H_pre_act": torch.empty(n, **f32),
-                 "H_post_act": torch.empty(n, **f32), "M": torch.empty(n, n, **f32)}
+        saved = {"rms": _empty(B, **f32), "H_pre_act": _empty(n, **f32),
+                 "H_post_act": _empty(n, **f32), "M": _empty(n, n, **f32)}
     nbytes = workspace_bytes(L.OP_STATIC_FWD, B, n, C, iters, tag)
     ws = _workspace(nbytes, dev, workspace)
     g = (lambda k: _ptr(saved[k])) if saved is not None else (lambda k: None)
@@ -163,9 +180,9 @@ def static_bwd(dy, x, rmsnorm_weight, H_res, saved, iters, eps, *, grads=None, d
     dev = x.device
     f32 = dict(dtype=torch.float32, device=dev)
     if grads is None:
-        grads = {"d_rmsnorm_weight": torch.empty(C, **f32), "d_H_pre": torch.empty(n, **f32),
-                 "d_H_post": torch.empty(n, **f32), "d_H_res": torch.empty(n, n, **f32)}
-    dx = torch.empty_like(x) if dx is None else _chk(dx, "dx", x.dtype, x.shape)
+        grads = {"d_rmsnorm_weight": _empty(C, **f32), "d_H_pre": _empty(n, **f32),
+                 "d_H_post": _empty(n, **f32), "d_H_res": _empty(n, n, **f32)}
+    dx = _empty_like(x) if dx is None else _chk(dx, "dx", x.dtype, x.shape)
     nbytes = workspace_bytes(L.OP_STATIC_BWD, B, n, C, iters, tag)
     ws = _workspace(nbytes, dev, workspace)
     st = L.lib().mhc_static_bwd(
@@ -184,7 +201,7 @@ def sinkhorn_fwd(inp, iters, eps):
         raise ValueError("sinkhorn expects [n,n] or [batch,n,n] square matrices")
     n = inp.shape[-1]
     batch = inp.shape[0] if inp.dim() == 3 else 1
-    out = torch.empty_like(inp)
+    out = _empty_like(inp)
     st = L.lib().mhc_sinkhorn_fwd(_ptr(out), _ptr(inp), batch, n, int(iters), float(eps), _stream())
     L.check(st, "mhc_sinkhorn_fwd")
     return out
@@ -196,7 +213,7 @@ def sinkhorn_bwd(grad_out, inp, iters, eps):
     _chk(grad_out, "grad_out", torch.float32, inp.shape)
     n = inp.shape[-1]
     batch = inp.shape[0] if inp.dim() == 3 else 1
-    d_inp = torch.empty_like(inp)
+    d_inp = _empty_like(inp)
     nbytes = workspace_bytes(L.OP_SINKHORN_BWD, batch, n, 0, iters, L.F32)
     ws = _workspace(nbytes, inp.device)
     st = L.lib().mhc_sinkhorn_bwd(_ptr(d_inp), _ptr(grad_out), _ptr(inp), batch, n, int(iters),
@@ -210,8 +227,8 @@ def rmsnorm_fwd(inp, weight, eps):
     _chk(inp, "inp", torch.bfloat16)
     B, Cc = inp.shape
     _chk(weight, "weight", torch.bfloat16, (Cc,))
-    out = torch.empty_like(inp)
-    rms = torch.empty(B, dtype=torch.float32, device=inp.device)
+    out = _empty_like(inp)
+    rms = _empty(B, dtype=torch.float32, device=inp.device)
     st = L.lib().mhc_rmsnorm_fwd(_ptr(out), _ptr(rms), _ptr(inp), _ptr(weight), B, Cc, float(eps), _stream())
     L.check(st, "mhc_rmsnorm_fwd")
     return out, rms
@@ -224,8 +241,8 @@ def rmsnorm_bwd(grad_out, inp, weight, rms):
     _chk(grad_out, "grad_out", torch.bfloat16, inp.shape)
     _chk(weight, "weight", torch.bfloat16, (Cc,))
     _chk(rms, "rms", torch.float32, (B,))
-    d_inp = torch.empty_like(inp)
-    d_w = torch.empty(Cc, dtype=torch.float32, device=inp.device)
+    d_inp = _empty_like(inp)
+    d_w = _empty(Cc, dtype=torch.float32, device=inp.device)
     nbytes = workspace_bytes(L.OP_RMSNORM_BWD, B, 1, Cc, 0, L.BF16)
     ws = _workspace(nbytes, inp.device)
     st = L.lib().mhc_rmsnorm_bwd(_ptr(d_inp), _ptr(d_w), _ptr(grad_out), _ptr(inp), _ptr(weight),

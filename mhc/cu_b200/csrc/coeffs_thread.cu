@@ -218,13 +218,15 @@ coeffs_dyn_bwd_lanes_kernel(float* __restrict__ dpr, float* __restrict__ qq,
     float d = elem ? dH[tok * K + k_res] : 0.f;
     const float* dn = den + tl * dpt;
     for (int t = iters - 1; t >= 0; --t) {
-        const float cd = dn[(2 * t + 1) * 4 + j];
+        // lanes outside the n x n matrix carry zeros; their slots of the saved denominators are
+        // never written, so they take 1 instead of reading them
+        const float cd = elem ? dn[(2 * t + 1) * 4 + j] : 1.f;
         float tc = d * y;
         tc += __shfl_xor_sync(0xffffffffu, tc, 4);
         tc += __shfl_xor_sync(0xffffffffu, tc, 8);
         d = (d - tc) * sk_rcp<float>(cd);
         y *= cd;
-        const float rd = dn[(2 * t) * 4 + i];
+        const float rd = elem ? dn[(2 * t) * 4 + i] : 1.f;
         float tr = d * y;
         tr += __shfl_xor_sync(0xffffffffu, tr, 1);
         tr += __shfl_xor_sync(0xffffffffu, tr, 2);

@@ -23,3 +23,13 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True, scope="session")
+def _poisoned_buffers():
+    """Buffers allocated by the ctypes wrappers start as NaN bytes during the tests, so that a read
+    of a slot no kernel wrote fails a parity check instead of depending on allocator history."""
+    from mhc.cu_b200 import capi
+    capi.POISON = True
+    yield
+    capi.POISON = False
