@@ -147,12 +147,6 @@ int dynamic_fwd_t(void* y, float* rms, float* rms_h, float* H_pre, float* H_post
     Carver c(workspace);
     DynFwdWs ws(c, d, dtype);
     if constexpr (std::is_same<T, bf16>::value) {
-        if (fwd_cluster_size(d) != 0) {
-            MHC_TRY(launch_fwd_cluster((bf16*)y, rms, rms_h, H_pre, H_post, M, proj, sk_den,
-                                       (const bf16*)x, (const bf16*)w, (const bf16*)phi, alpha, bias,
-                                       nullptr, d, iters, eps, s));
-            return MHC_OK;
-        }
         if (proj_mma_splits(d) != 0)
             MHC_TRY(launch_proj_mma(ws.praw, ws.sumsq, (const bf16*)x, (const bf16*)phi, d, s));
         else

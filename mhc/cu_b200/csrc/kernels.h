@@ -155,13 +155,6 @@ cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, c
                                   const float* H_post, const float* M, int* status, Dims d,
                                   float eps, cudaStream_t s);
 
-// ---- fwd_cluster.cu: whole dynamic forward in one cluster kernel (bf16, n = 4) ----------------
-int fwd_cluster_size(Dims d);   // blocks per cluster for this shape, 0 = not covered
-cudaError_t launch_fwd_cluster(bf16* y, float* rho, float* rms_h, float* H_pre, float* H_post,
-                               float* M, float* proj, float* sk_den, const bf16* x, const bf16* w,
-                               const bf16* phi, const float* alpha, const float* bias, int* status,
-                               Dims d, int iters, float eps, cudaStream_t s);
-
 // ---- mix_bwd.cu: backward pass A with the token's x and dy rows staged by bulk async copies ---
 bool bwd_reduce_staged_supported(Dims d, size_t elem_bytes);
 template <typename T>

@@ -83,6 +83,8 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
 #ifdef MHC_PHASE_CLOCKS
     long long stamp[8];
     int nstamp = 0;
+    unsigned long long gt_begin;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt_begin));
 #define MHC_STAMP() stamp[nstamp++] = clock64()
 #else
 #define MHC_STAMP()
@@ -92,46 +94,82 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
     if (tid == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
+    }
+    // Static coefficients: the row copy starts at once.  Dynamic: every block of the single wave
+    // starts together, and small loads issued behind 26 MB of row copies wait for them; so the
+    // partial results, alpha and the biases are fetched first and the row copy is issued when
+    // they have arrived (it then lands while the Sinkhorn thread works).
+    if (!DYN && tid == 0) {
         mbar_arrive_expect_tx(bar, row_bytes);
         bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
     }
 
     if constexpr (DYN) {
         // 1a. sum the split partial results of this token
-        for (int k = tid; k <= K; k += kMixThreads) {
-            const float* src = (k < K) ? p.praw + b * K + k : p.sumsq + b;
-            const int64_t st = (k < K) ? p.B * K : p.B;
+        if (2 * (K + 1) <= kMixThreads) {
+            // two adjacent threads per value, eight loads in flight each: one or two round trips
+            // for up to 32 partial results; the association of the sum is fixed
+            const int k = tid >> 1, l = tid & 1;
             float v = 0.f;
-            int s = 0;
-            for (; s + 4 <= p.nsplit; s += 4) {   // four loads in flight per round trip
-                const float a0 = src[(s + 0) * st], a1 = src[(s + 1) * st];
-                const float a2 = src[(s + 2) * st], a3 = src[(s + 3) * st];
-                v += (a0 + a1) + (a2 + a3);
+            if (k <= K) {
+                const float* src = (k < K) ? p.praw + b * K + k : p.sumsq + b;
+                const int64_t st = (k < K) ? p.B * K : p.B;
+                for (int s0 = l; s0 < p.nsplit; s0 += 16) {
+                    float a[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int s = s0 + 2 * u;
+                        a[u] = (s < p.nsplit) ? src[s * st] : 0.f;
+                    }
+                    v += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
+                }
             }
-            for (; s < p.nsplit; ++s) v += src[s * st];
-            cf[k] = v;
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            if (k <= K && l == 0) cf[k] = v;
+        } else {
+            for (int k = tid; k <= K; k += kMixThreads) {
+                const float* src = (k < K) ? p.praw + b * K + k : p.sumsq + b;
+                const int64_t st = (k < K) ? p.B * K : p.B;
+                float v = 0.f;
+                int s = 0;
+                for (; s + 4 <= p.nsplit; s += 4) {   // four loads in flight per round trip
+                    const float a0 = src[(s + 0) * st], a1 = src[(s + 1) * st];
+                    const float a2 = src[(s + 2) * st], a3 = src[(s + 3) * st];
+                    v += (a0 + a1) + (a2 + a3);
+                }
+                for (; s < p.nsplit; ++s) v += src[s * st];
+                cf[k] = v;
+            }
         }
+        // alpha and the bias of this thread's output ride the same round trip as the partials
+        const float al0 = p.alpha[0], al1 = p.alpha[1], al2 = p.alpha[2];
+        const float bias_k = (tid < K) ? p.bias[tid] : 0.f;
         __syncthreads();
+        if (tid == 0) {
+            mbar_arrive_expect_tx(bar, row_bytes);
+            bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
+        }
         MHC_STAMP();
         // 1b. activations, one output per thread
         const A r = mix_sqrt<A>(A(cf[K]) / A(n * C) + A(p.eps));
         const A rinv = A(1) / r;
         for (int k = tid; k < K; k += kMixThreads) {
             const A pv = A(cf[k]) * rinv;
+            const A bk = A(k == tid ? bias_k : p.bias[k]);
             p.proj[b * K + k] = (float)pv;
             if (k < n) {
-                const float h = (float)sk_sigmoid<A>(A(p.alpha[0]) * pv + A(p.bias[k]));
+                const float h = (float)sk_sigmoid<A>(A(al0) * pv + bk);
                 cfc[k] = h;
                 p.H_pre[b * n + k] = h;
             } else if (k < 2 * n) {
-                const float h = (float)(A(2) * sk_sigmoid<A>(A(p.alpha[1]) * pv + A(p.bias[k])));
+                const float h = (float)(A(2) * sk_sigmoid<A>(A(al1) * pv + bk));
                 cfc[MAXN + (k - n)] = h;
                 p.H_post[b * n + (k - n)] = h;
             } else {
                 // E kept in fp32 shared memory; the Sinkhorn thread widens it again
                 const int e = k - 2 * n;
                 cfc[2 * MAXN + (e / n) * MAXN + (e % n)] =
-                    (float)sk_exp<A>(A(p.alpha[2]) * pv + A(p.bias[k]));
+                    (float)sk_exp<A>(A(al2) * pv + bk);
             }
         }
         if (tid == 0) p.rms_h[b] = (float)r;
@@ -264,6 +302,17 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
     __syncthreads();
     if (b == 7 && tid == 0 && p.rms_h != nullptr)
         for (int i = 0; i < nstamp; ++i) reinterpret_cast<long long*>(p.rms_h)[16 + i] = stamp[i] - stamp[0];
+    // ... and every block overwrites its row of proj with its start / end time and SM
+    if (DYN && tid == 0 && K >= 6) {
+        unsigned long long gt1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt1));
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        long long* o = reinterpret_cast<long long*>(p.proj + b * K);
+        o[0] = (long long)gt_begin;
+        o[1] = (long long)gt1;
+        o[2] = smid;
+    }
 #endif
 #undef MHC_STAMP
 }
