@@ -179,7 +179,10 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
                   Dims d, int iters, float eps, int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     DynBwdWs ws(c, d, iters, dtype);
-    if (bwd_reduce_staged_supported(d, sizeof(T)))
+    if (std::is_same<T, bf16>::value && bwd_gram_supported(d))
+        MHC_TRY(launch_bwd_gram(ws.dH, ws.c2, (const bf16*)x, (const bf16*)dy, (const bf16*)w, H_pre,
+                                H_post, 1, rms, d, s));
+    else if (bwd_reduce_staged_supported(d, sizeof(T)))
         MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
                                             H_pre, H_post, 1, rms, nullptr, d, s));
     else if (d.n > 8)
@@ -264,7 +267,10 @@ int static_bwd_t(void* dx, float* d_w, float* d_H_pre, float* d_H_post, float* d
                  int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     StaticBwdWs ws(c, d, iters, dtype);
-    if (bwd_reduce_staged_supported(d, sizeof(T)))
+    if (std::is_same<T, bf16>::value && bwd_gram_supported(d))
+        MHC_TRY(launch_bwd_gram(ws.dH, ws.c2, (const bf16*)x, (const bf16*)dy, (const bf16*)w, hp, hq,
+                                0, rms, d, s));
+    else if (bwd_reduce_staged_supported(d, sizeof(T)))
         MHC_TRY(launch_bwd_reduce_staged<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w,
                                             hp, hq, 0, rms, nullptr, d, s));
     else if (d.n > 8)

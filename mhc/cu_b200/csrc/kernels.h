@@ -155,6 +155,12 @@ cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, c
                                   const float* H_post, const float* M, int* status, Dims d,
                                   float eps, cudaStream_t s);
 
+// ---- bwd_gram.cu: backward pass A from tensor-core Gram matrices (bf16, n = 4) --------------
+bool bwd_gram_supported(Dims d);
+cudaError_t launch_bwd_gram(float* dH, float* c2, const bf16* x, const bf16* g, const bf16* w,
+                            const float* H_pre, const float* H_post, int coef_stride,
+                            const float* rms, Dims d, cudaStream_t s);
+
 // ---- mix_bwd.cu: backward pass A with the token's x and dy rows staged by bulk async copies ---
 bool bwd_reduce_staged_supported(Dims d, size_t elem_bytes);
 template <typename T>

@@ -93,20 +93,23 @@ proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
     float sslo = 0.f, sshi = 0.f;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
 
+    // A batch is kCH * 32 = 128 reduction elements, walked as two 64-element pieces: the four
+    // lanes of a row take 32 contiguous bytes each (two 16-byte loads), so that a warp's loads
+    // cover whole 128-byte lines of its rows.
     for (int b = 0; b < nb; ++b) {
-        const int64_t k0 = kbeg + (int64_t)b * (kCH * kChunk) + 8 * q;
-        if (k0 - 8 * q >= nC) break;
+        const int64_t kb = kbeg + (int64_t)b * (kCH * kChunk);
+        if (kb >= nC) break;
         uint4 r[kCH], s[kCH], pf[kCH][NT];
 #pragma unroll
         for (int c = 0; c < kCH; ++c) {
-            const int64_t k = k0 + c * kChunk;
+            const int64_t k = kb + (c >> 1) * 64 + 16 * q + 8 * (c & 1);
             const bool in = k < nC;  // nC is a multiple of 8, so a started vector is a whole vector
             r[c] = (in && vlo) ? ldg_stream(xlo + k) : zero;
             s[c] = (in && vhi) ? ldg_stream(xhi + k) : zero;
         }
 #pragma unroll
         for (int c = 0; c < kCH; ++c) {
-            const int64_t k = k0 + c * kChunk;
+            const int64_t k = kb + (c >> 1) * 64 + 16 * q + 8 * (c & 1);
             const bool in = k < nC;
 #pragma unroll
             for (int t = 0; t < NT; ++t)
