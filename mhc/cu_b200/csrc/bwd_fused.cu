@@ -4,10 +4,13 @@
 //   dx[b,j,c]   = sum_i M[i,j] g[i,c] + H_pre[j] da[c] - qq x[j,c] + sum_k dpr[b,k] phi[k, jC+c]
 //   dphi[k,jC+c] += sum_b dpr[b,k] x[b,j,c]          dw[c] += (sum_i H_post[i] g[i,c]) a[c] / rho
 //
-// Block = 4 warps, one block of 32 columns (of all N streams) and a range of token groups
-// (16 tokens each).  Per group the [16 tokens x N streams x 32 columns] tiles of x and dy and the
-// 16 token records are brought into shared memory with cp.async, double buffered, so the next
-// group's loads are in flight while this one is computed.  Warp w owns columns [8w, 8w+8):
+// Block = 8 warps, one block of 64 columns (of all N streams: 128-byte lines of every row; with
+// 32-column blocks every load and store touched half lines and the kernel ran a quarter slower)
+// and a range of token groups (16 tokens each).  Per group the [16 tokens x N streams x 64
+// columns] tiles of x and dy and the 16 token records are brought into shared memory with
+// cp.async, three stages deep, so the next groups' loads are in flight while this one is
+// computed.  dx is assembled in place of the x tile and leaves the block as whole lines.
+// Warp w owns columns [8w, 8w+8):
 //   * dpr x phi  on mma.sync.m16n8k16 (+k8): A = dpr (16 tokens x K), B = phi fragments held in
 //     registers for the whole block; the accumulator of thread (g,q) is (tokens g, g+8) x
 //     (columns 2q, 2q+1), and the same thread finishes those outputs element-wise;
@@ -64,8 +67,8 @@ __device__ __forceinline__ uint32_t f_ldg_u32(const bf16* p) {
     return *reinterpret_cast<const uint32_t*>(p);
 }
 
-constexpr int kFWarps = 4;
-constexpr int kFCols = 32;
+constexpr int kFWarps = 8;
+constexpr int kFCols = 64;
 constexpr int kFTok = 16;
 
 template <int N>
@@ -86,7 +89,7 @@ struct FusedCfg {
 };
 
 template <int N>
-__global__ void __launch_bounds__(kFWarps * 32, 3)
+__global__ void __launch_bounds__(kFWarps * 32, 2)
 dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __restrict__ dw_part,
                const bf16* __restrict__ x, const bf16* __restrict__ gy,
                const bf16* __restrict__ w, const float* __restrict__ rec,
@@ -152,7 +155,8 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
     // Each thread always copies the same chunks of a stage: x / dy chunks tid and tid+128 of the
     // 16 x N x 4 grid (token, stream, 8-column part) and, for tid < 16*RS/4, one record chunk.
     // Everything that does not depend on the group is computed once, here.
-    constexpr int NCHUNK = kFTok * N * 4;
+    constexpr int PARTS = kFCols / 8;              // 16-byte parts of a (token, stream) segment
+    constexpr int NCHUNK = kFTok * N * PARTS;
     constexpr int PER_THREAD = (NCHUNK + kFWarps * 32 - 1) / (kFWarps * 32);
     int64_t src_off[PER_THREAD];     // element offset inside a group (token part added per group)
     int dst_off[PER_THREAD];         // byte offset inside a tile
@@ -161,7 +165,7 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
 #pragma unroll
     for (int u = 0; u < PER_THREAD; ++u) {
         const int c = tid + u * kFWarps * 32;
-        const int part = c & 3, j = (c >> 2) % N, t = c / (4 * N);
+        const int part = c % PARTS, j = (c / PARTS) % N, t = c / (PARTS * N);
         chunk_tok[u] = (c < NCHUNK) ? t : -1;
         chunk_col_in[u] = (c0 + 8 * part) < C;
         src_off[u] = (int64_t)t * nC + (int64_t)j * C + (chunk_col_in[u] ? c0 + 8 * part : 0);
@@ -216,8 +220,6 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
         else f_cp_async_wait<0>();
         __syncthreads();   // every thread's copies of this stage have landed
 
-        const int64_t tok[2] = {grp * kFTok + g, grp * kFTok + g + 8};
-        const bool tv[2] = {tok[0] < B, tok[1] < B};
         const unsigned char* xs = smem + (size_t)buf * BUFB;
         const unsigned char* gs = xs + TILEB;
         const float* rs = reinterpret_cast<const float*>(xs + 2 * TILEB);
@@ -316,9 +318,21 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
                     o0 = fmaf(mji, gv[i][0], o0);
                     o1 = fmaf(mji, gv[i][1], o1);
                 }
-                if (tv[h] && colin)
-                    *reinterpret_cast<uint32_t*>(dx + tok[h] * nC + (int64_t)j * C + cw + 2 * q) =
-                        pack_bf16x2(o0, o1);
+                // dx replaces x in the tile (this thread is the only reader of these elements and
+                // has read them all); the block then writes whole 128-byte lines
+                *reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(xs) + t * TOKB +
+                                             j * (kFCols * 2) + warp * 16 + q * 4) =
+                    pack_bf16x2(o0, o1);
+            }
+        }
+        __syncthreads();   // the dx tile is complete
+        {
+            const int64_t t0 = grp * kFTok;
+#pragma unroll
+            for (int u = 0; u < PER_THREAD; ++u) {
+                if (chunk_tok[u] >= 0 && (t0 + chunk_tok[u] < B) && chunk_col_in[u])
+                    *reinterpret_cast<uint4*>(dx + t0 * nC + src_off[u]) =
+                        *reinterpret_cast<const uint4*>(xs + dst_off[u]);
             }
         }
         __syncthreads();   // the stage may be overwritten by the prefetch of the next iteration
@@ -365,7 +379,7 @@ bool bwd_fused_supported(Dims d) { return d.n == 4 && d.C % 8 == 0 && d.nC() % 4
 static int fused_groups_per_block(Dims d) {
     const int64_t colblocks = (d.C + kFCols - 1) / kFCols;
     const int64_t groups = (d.B + kFTok - 1) / kFTok;
-    int64_t split = (3 * 148) / colblocks;   // at most three blocks per SM: one resident wave
+    int64_t split = (2 * 148) / colblocks;   // two blocks per SM: one resident wave
     if (split < 1) split = 1;
     if (split > groups) split = groups;
     return (int)((groups + split - 1) / split);
@@ -392,6 +406,9 @@ cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float*
     const size_t smem = (size_t)Cfg::STAGES * Cfg::BUFB;
     // with a single token range the partial IS the result
     float* part = (ntb == 1) ? dphi : dphi_part;
+    cudaError_t e = cudaFuncSetAttribute(dx_dphi_kernel<4>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
     dx_dphi_kernel<4><<<grid, kFWarps * 32, smem, s>>>(dx, part, dw_part, x, g, w, rec, dprb, dprT,
                                                         phi, d.B, Bp, d.C, gpb);
     return launched();
