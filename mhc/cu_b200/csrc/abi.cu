@@ -89,7 +89,8 @@ struct DynBwdWs {
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
         mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
         nblk = d.n <= 8 ? coeffs_thread_blocks(d) : coeffs_dyn_bwd_blocks(d);
-        const int nblk_max = nblk > coeffs_lanes_blocks(d) ? nblk : coeffs_lanes_blocks(d);
+        int nblk_max = nblk > coeffs_lanes_blocks(d) ? nblk : coeffs_lanes_blocks(d);
+        if (bwd_gram_supported(d) && bwd_gram_blocks(d) > nblk_max) nblk_max = bwd_gram_blocks(d);
         fused = mma && bwd_fused_supported(d);
         ntb = fused ? bwd_fused_token_blocks(d) : (mma ? dx_mma_token_blocks(d) : dx_token_blocks(d));
         if (d.n > 8) ntb = (int)d.B;   // the wide dx pass leaves one d_weight row per token
@@ -179,7 +180,22 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
                   Dims d, int iters, float eps, int dtype, void* workspace, cudaStream_t s) {
     Carver c(workspace);
     DynBwdWs ws(c, d, iters, dtype);
-    if (std::is_same<T, bf16>::value && bwd_gram_supported(d))
+    MmaBwdOut mo;
+    if (ws.mma) {
+        mo.rec = ws.rec; mo.dprb = ws.dprb; mo.dprT = ws.dprT; mo.M = M; mo.rms = rms; mo.c2 = ws.c2;
+    }
+    // the forward leaves its Sinkhorn denominators only on the bf16 fused path
+    const bool lanes = sk_den != nullptr && dtype == MHC_BF16 && mix_fwd_supported(d, sizeof(T)) &&
+                       coeffs_lanes_supported(d, iters);
+    // pass A and the coefficient backward in one launch where both tensor-core paths apply
+    const bool gram_fused = lanes && std::is_same<T, bf16>::value && bwd_gram_supported(d) && ws.mma;
+    if (gram_fused) {
+        GramFuse gf;
+        gf.dpr = ws.dpr; gf.qq = ws.qq; gf.partials = ws.partials; gf.M = M; gf.proj = proj;
+        gf.rms_h = rms_h; gf.alpha = alpha; gf.sk_den = sk_den; gf.iters = iters; gf.mo = mo;
+        MHC_TRY(launch_bwd_gram(ws.dH, ws.c2, (const bf16*)x, (const bf16*)dy, (const bf16*)w, H_pre,
+                                H_post, 1, rms, d, s, &gf));
+    } else if (std::is_same<T, bf16>::value && bwd_gram_supported(d))
         MHC_TRY(launch_bwd_gram(ws.dH, ws.c2, (const bf16*)x, (const bf16*)dy, (const bf16*)w, H_pre,
                                 H_post, 1, rms, d, s));
     else if (bwd_reduce_staged_supported(d, sizeof(T)))
@@ -191,14 +207,9 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
     else
         MHC_TRY(launch_bwd_reduce<T>(ws.dH, ws.c2, (const T*)x, (const T*)dy, (const bf16*)w, H_pre,
                                      H_post, 1, rms, d, s));
-    MmaBwdOut mo;
-    if (ws.mma) {
-        mo.rec = ws.rec; mo.dprb = ws.dprb; mo.dprT = ws.dprT; mo.M = M; mo.rms = rms; mo.c2 = ws.c2;
-    }
-    // the forward leaves its Sinkhorn denominators only on the bf16 fused path
-    const bool lanes = sk_den != nullptr && dtype == MHC_BF16 && mix_fwd_supported(d, sizeof(T)) &&
-                       coeffs_lanes_supported(d, iters);
-    if (lanes)
+    if (gram_fused) {
+        // done above
+    } else if (lanes)
         MHC_TRY(launch_coeffs_dyn_bwd_lanes(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, M, proj,
                                             rms_h, alpha, bias, sk_den, d, iters, mo, s));
     else if (d.n <= 8)
@@ -236,7 +247,8 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
         dsum.total4 = (int64_t)d.K() * d.nC() / 4;
     }
     MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials,
-                            lanes ? coeffs_lanes_blocks(d) : ws.nblk, d.n, s, dsum));
+                            gram_fused ? bwd_gram_blocks(d) : lanes ? coeffs_lanes_blocks(d) : ws.nblk,
+                            d.n, s, dsum));
     return MHC_OK;
 }
 

@@ -9,7 +9,7 @@
 //     s     = <u, a>      = sum_ij H_post[i] H_pre[j] Gw[i][j]
 // Output, as from the scalar pass: dH[b][K] = (dH_pre, dH_post, dM), c2[b] = s / (C rho^3).
 //
-// One block = two tokens = the eight rows (token, stream) of x and of dy, its eight warps splitting
+// One block = two tokens = the eight rows (token, stream) of x and of dy, its four warps splitting
 // the columns.  Per 64 columns a thread loads 32 contiguous bytes of "its" row of dy, of x and of
 // w (the four lanes of a row cover a whole 128-byte line: with 16 bytes per lane the same kernel ran
 // a third slower) and issues, per 16 bytes, four m16n8k16 MMAs:
@@ -28,13 +28,14 @@
 // per-token coefficients.
 #include <cuda_bf16.h>
 
+#include "coeffs_lanes.cuh"
 #include "kernels.h"
 
 namespace mhc {
 
 namespace {
 
-constexpr int kGWarps = 8;
+constexpr int kGWarps = 4;
 constexpr int kGBatch = 3;   // chunks of 64 columns whose loads are in flight together
 
 __device__ __forceinline__ void g_mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -60,14 +61,22 @@ __device__ __forceinline__ uint32_t g_mul_bf16x2(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-__global__ void __launch_bounds__(kGWarps * 32)
+// FUSE: the block also runs the backward of its two tokens' coefficients (coeffs_lanes.cuh) on
+// warp 0 once the inner products are known, instead of leaving dH to a second kernel.
+template <bool FUSE>
+__global__ void __launch_bounds__(kGWarps * 32, 6)
 bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* __restrict__ x,
                 const bf16* __restrict__ g, const bf16* __restrict__ w,
                 const float* __restrict__ H_pre, const float* __restrict__ H_post,
-                const float* __restrict__ rms, int64_t B, int64_t C, int coef_stride) {
+                const float* __restrict__ rms, int64_t B, int64_t C, int coef_stride,
+                const GramFuse f) {
     __shared__ float part[kGWarps][2][3][16];   // [warp][token][G, Gw, X2][i*4+j]
     __shared__ float tot[2][3][16];
     __shared__ float coef[2][12];               // hp[4] hq[4] 1/rho
+    __shared__ float dHs[2][24];                // FUSE: the tokens' dH and c2 stay in the block
+    __shared__ float c2s[2];
+    __shared__ float pts[2][28];                // FUSE: the tokens' terms of d_bias and d_alpha
+    extern __shared__ __align__(16) float den[];   // FUSE: [2 tokens][2*iters][4] saved denominators
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, q = lane & 3;     // fragment row / column group
     const int64_t pair = blockIdx.x;
@@ -86,6 +95,31 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
             v = k < 4 ? H_pre[cb * 4 + k] : k < 8 ? H_post[cb * 4 + (k - 4)] : 1.f / rms[b];
         }
         coef[t][k] = v;
+    }
+
+    // FUSE: what the coefficient backward needs besides dH is fetched now as well
+    const int tl = lane >> 4, e = lane & 15;    // warp 0: token slot and matrix element of a lane
+    const int64_t tokf = pair * 2 + tl;
+    LaneIn lin{0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float rh = 1.f, al0 = 0.f, al1 = 0.f, al2 = 0.f;
+    if constexpr (FUSE) {
+        const int dpt = 2 * f.iters * 4;
+        const int64_t base = pair * 2 * dpt, lim = B * dpt;
+        for (int k = tid; k < 2 * dpt; k += kGWarps * 32)
+            den[k] = (base + k < lim) ? f.sk_den[base + k] : 1.f;
+        if (tid < 56) (&pts[0][0])[tid] = 0.f;
+        if (warp == 0 && tokf < B) {
+            lin.m = f.M[tokf * 16 + e];
+            lin.p_res = f.proj[tokf * 24 + 8 + e];
+            if (e < 8) {
+                lin.h = e < 4 ? H_pre[tokf * 4 + e] : H_post[tokf * 4 + (e - 4)];
+                lin.p_e = f.proj[tokf * 24 + e];
+            }
+            rh = f.rms_h[tokf];
+            al0 = f.alpha[0];
+            al1 = f.alpha[1];
+            al2 = f.alpha[2];
+        }
     }
 
     float acc1[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};
@@ -176,7 +210,27 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
             } else {
                 o = G[k - 8];
             }
-            dH[b * 24 + k] = o;
+            if constexpr (FUSE) {
+                dHs[t][k] = o;
+                if (k == 0) c2s[t] = c2;
+            } else {
+                dH[b * 24 + k] = o;
+            }
+        }
+    }
+    if constexpr (FUSE) {
+        __syncthreads();
+        if (warp == 0) {
+            const bool act = tokf < B;
+            if (act) {
+                lin.dres = dHs[tl][8 + e];
+                if (e < 8) lin.dh = dHs[tl][e];
+            }
+            coeffs_lanes_token(tokf, act, e, 4, 4 * C, f.iters, B, lin, rh, al0, al1, al2,
+                               coef[tl][8], act ? c2s[tl] : 0.f, den + tl * 2 * f.iters * 4, pts[tl],
+                               f.dpr, f.qq, f.mo);
+            __syncwarp();
+            if (lane < 27) f.partials[(int64_t)pair * 27 + lane] = pts[0][lane] + pts[1][lane];
         }
     }
 }
@@ -185,14 +239,25 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
 
 bool bwd_gram_supported(Dims d) { return d.n == 4 && d.C % 64 == 0; }
 
+// two tokens per block, up to the batch rounded to 16 tokens: the fused variant also zeroes the
+// padding columns of the transposed bf16 copy of dpr that the next pass reads
+int bwd_gram_blocks(Dims d) { return (int)((d.B + 15) / 16 * 8); }
+
 cudaError_t launch_bwd_gram(float* dH, float* c2, const bf16* x, const bf16* g, const bf16* w,
                             const float* H_pre, const float* H_post, int coef_stride,
-                            const float* rms, Dims d, cudaStream_t s) {
+                            const float* rms, Dims d, cudaStream_t s, const GramFuse* fuse) {
     if (d.B == 0) return cudaSuccess;
     if (!bwd_gram_supported(d)) return cudaErrorNotSupported;
-    const unsigned grid = (unsigned)((d.B + 1) / 2);
-    bwd_gram_kernel<<<grid, kGWarps * 32, 0, s>>>(dH, c2, x, g, w, H_pre, H_post, rms, d.B, d.C,
-                                                  coef_stride);
+    const unsigned grid = (unsigned)bwd_gram_blocks(d);
+    if (fuse != nullptr) {
+        const size_t smem = (size_t)2 * 2 * fuse->iters * 4 * sizeof(float);
+        if (smem > 40 * 1024) return cudaErrorNotSupported;
+        bwd_gram_kernel<true><<<grid, kGWarps * 32, smem, s>>>(dH, c2, x, g, w, H_pre, H_post, rms,
+                                                               d.B, d.C, coef_stride, *fuse);
+    } else {
+        bwd_gram_kernel<false><<<grid, kGWarps * 32, 0, s>>>(dH, c2, x, g, w, H_pre, H_post, rms, d.B,
+                                                             d.C, coef_stride, GramFuse());
+    }
     return launched();
 }
 

@@ -7,6 +7,7 @@
 // Same inputs / outputs as coeffs_dyn_bwd_kernel in coeffs.cu (which remains for n > 8).
 #include "kernels.h"
 #include "sinkhorn.cuh"
+#include "coeffs_lanes.cuh"
 
 namespace mhc {
 
@@ -194,8 +195,7 @@ coeffs_dyn_bwd_lanes_kernel(float* __restrict__ dpr, float* __restrict__ qq,
                             const float* __restrict__ bias, const float* __restrict__ sk_den,
                             int64_t B, int n, int64_t nC, int iters, MmaBwdOut mo) {
     extern __shared__ __align__(16) float sm[];   // [16][K+3] token sums, then [16][2*iters*4] den
-    const int K = 2 * n + n * n, KP = K + 3, K8P = (K + 7) / 8 * 8;
-    const int64_t Bp = (B + 15) / 16 * 16;
+    const int K = 2 * n + n * n, KP = K + 3;
     const int tl = threadIdx.x >> 4, e = threadIdx.x & 15;   // token slot, element
     const int i = e >> 2, j = e & 3;
     const int64_t tok = (int64_t)blockIdx.x * kLaneTokens + tl;
@@ -213,95 +213,23 @@ coeffs_dyn_bwd_lanes_kernel(float* __restrict__ dpr, float* __restrict__ qq,
     }
     __syncthreads();
 
-    const int k_res = 2 * n + i * n + j;
-    float y = elem ? M[tok * n * n + i * n + j] : 0.f;
-    float d = elem ? dH[tok * K + k_res] : 0.f;
-    const float* dn = den + tl * dpt;
-    for (int t = iters - 1; t >= 0; --t) {
-        // lanes outside the n x n matrix carry zeros; their slots of the saved denominators are
-        // never written, so they take 1 instead of reading them
-        const float cd = elem ? dn[(2 * t + 1) * 4 + j] : 1.f;
-        float tc = d * y;
-        tc += __shfl_xor_sync(0xffffffffu, tc, 4);
-        tc += __shfl_xor_sync(0xffffffffu, tc, 8);
-        d = (d - tc) * sk_rcp<float>(cd);
-        y *= cd;
-        const float rd = elem ? dn[(2 * t) * 4 + i] : 1.f;
-        float tr = d * y;
-        tr += __shfl_xor_sync(0xffffffffu, tr, 1);
-        tr += __shfl_xor_sync(0xffffffffu, tr, 2);
-        d = (d - tr) * sk_rcp<float>(rd);
-        y *= rd;
-    }
-    // y is now E = exp(t_res) (rebuilt), d = dL/dE
-    const float r = act ? rms_h[tok] : 1.f;
-    const float rinv = 1.f / r;
-    const int RS = (n * n + 2 * n + 3 + 3) / 4 * 4;
-    float* rc = (mo.rec != nullptr && act) ? mo.rec + tok * RS : nullptr;
-    float qacc = 0.f, dal0 = 0.f, dal1 = 0.f, dal2 = 0.f;
-    float* pt = part + tl * KP;
+    LaneIn in{0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (elem) {
-        const float dtr = d * y;
-        const float pv = proj[tok * K + k_res];
-        const float v = alpha[2] * dtr * rinv;
-        dpr[tok * K + k_res] = v;
-        pt[k_res] = dtr;
-        qacc = v * pv;
-        dal2 = dtr * pv;
-        if (rc != nullptr) {
-            rc[j * n + i] = M[tok * n * n + i * n + j];   // MT[j][i] = M[i][j]
-            mo.dprb[tok * K8P + k_res] = __float2bfloat16_rn(v);
-            mo.dprT[(int64_t)k_res * Bp + tok] = __float2bfloat16_rn(v);
-        }
+        const int k_res = 2 * n + i * n + j;
+        in.m = M[tok * n * n + i * n + j];
+        in.dres = dH[tok * K + k_res];
+        in.p_res = proj[tok * K + k_res];
     }
-    if (act && e < 2 * n) {   // lanes 0..n-1: the pre entries, n..2n-1: the post entries
-        const bool post = e >= n;
-        const int ii = post ? e - n : e;
-        const float h = post ? H_post[tok * n + ii] : H_pre[tok * n + ii];
-        const float pv = proj[tok * K + e];
-        const float dh = dH[tok * K + e];
-        const float dt = post ? dh * h * (1.f - 0.5f * h) : dh * h * (1.f - h);
-        const float v = alpha[post ? 1 : 0] * dt * rinv;
-        dpr[tok * K + e] = v;
-        pt[e] = dt;
-        qacc += v * pv;
-        if (post) dal1 = dt * pv; else dal0 = dt * pv;
-        if (rc != nullptr) {
-            rc[n * n + e] = h;   // H_pre at n*n + i, H_post at n*n + n + i
-            mo.dprb[tok * K8P + e] = __float2bfloat16_rn(v);
-            mo.dprT[(int64_t)e * Bp + tok] = __float2bfloat16_rn(v);
-        }
+    if (act && e < 2 * n) {
+        in.h = (e >= n) ? H_post[tok * n + (e - n)] : H_pre[tok * n + e];
+        in.dh = dH[tok * K + e];
+        in.p_e = proj[tok * K + e];
     }
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) {
-        qacc += __shfl_xor_sync(0xffffffffu, qacc, o);
-        dal0 += __shfl_xor_sync(0xffffffffu, dal0, o);
-        dal1 += __shfl_xor_sync(0xffffffffu, dal1, o);
-        dal2 += __shfl_xor_sync(0xffffffffu, dal2, o);
-    }
-    if (act && e == 0) {
-        const float qv = qacc / ((float)nC * r);
-        qq[tok] = qv;
-        pt[K] = dal0;
-        pt[K + 1] = dal1;
-        pt[K + 2] = dal2;
-        if (rc != nullptr) {
-            rc[n * n + 2 * n] = 1.f / mo.rms[tok];
-            rc[n * n + 2 * n + 1] = mo.c2[tok];
-            rc[n * n + 2 * n + 2] = qv;
-        }
-    }
-    if (mo.rec != nullptr && tok < Bp) {
-        // zero padding of the bf16 copies: rows K..K8P-1, and all rows of the tokens B..Bp-1
-        for (int k = e; k < K8P; k += 16) {
-            if (!act) {
-                mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn(0.f);
-            } else if (k >= K) {
-                mo.dprb[tok * K8P + k] = __float2bfloat16_rn(0.f);
-                mo.dprT[(int64_t)k * Bp + tok] = __float2bfloat16_rn(0.f);
-            }
-        }
-    }
+    const float r = act ? rms_h[tok] : 1.f;
+    const float c1 = (act && mo.rec != nullptr) ? 1.f / mo.rms[tok] : 0.f;
+    const float c2v = (act && mo.rec != nullptr) ? mo.c2[tok] : 0.f;
+    coeffs_lanes_token(tok, act, e, n, nC, iters, B, in, r, alpha[0], alpha[1], alpha[2], c1, c2v,
+                       den + tl * dpt, part + tl * KP, dpr, qq, mo);
     __syncthreads();
     for (int k = threadIdx.x; k < KP; k += 256) {
         float t = 0.f;

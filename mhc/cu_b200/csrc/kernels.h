@@ -157,9 +157,26 @@ cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, c
 
 // ---- bwd_gram.cu: backward pass A from tensor-core Gram matrices (bf16, n = 4) --------------
 bool bwd_gram_supported(Dims d);
+int bwd_gram_blocks(Dims d);   // rows of `partials` the fused variant writes
+// With `fuse` the kernel also runs the coefficient backward of its tokens (dynamic H, saved
+// Sinkhorn denominators): dH stays in the block, and dpr, qq, partials[bwd_gram_blocks][K+3]
+// and the MmaBwdOut records are written as by launch_coeffs_dyn_bwd_lanes.
+struct GramFuse {
+    float* dpr = nullptr;
+    float* qq = nullptr;
+    float* partials = nullptr;
+    const float* M = nullptr;
+    const float* proj = nullptr;
+    const float* rms_h = nullptr;
+    const float* alpha = nullptr;
+    const float* sk_den = nullptr;
+    int iters = 0;
+    MmaBwdOut mo;
+};
 cudaError_t launch_bwd_gram(float* dH, float* c2, const bf16* x, const bf16* g, const bf16* w,
                             const float* H_pre, const float* H_post, int coef_stride,
-                            const float* rms, Dims d, cudaStream_t s);
+                            const float* rms, Dims d, cudaStream_t s,
+                            const GramFuse* fuse = nullptr);
 
 // ---- mix_bwd.cu: backward pass A with the token's x and dy rows staged by bulk async copies ---
 bool bwd_reduce_staged_supported(Dims d, size_t elem_bytes);

@@ -103,6 +103,34 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
         mbar_arrive_expect_tx(bar, row_bytes);
         bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
     }
+    if (tid == 0) {
+        red[0] = 0.f;
+        red[2] = 0.f;   // "row copy failed" flag of the dynamic path
+    }
+    const int64_t nvec = C / V;
+    // pass 1 over the row block in shared memory: sum of squares of a = sum_i H_pre[i] x[i,:] over
+    // the vectors first, first + stride, ...
+    auto pass1 = [&](int first, int stride, const float (&hpv)[MAXN]) -> float {
+        float ss = 0.f;
+#pragma unroll 2
+        for (int64_t v = first; v < nvec; v += stride) {
+            float a[V];
+#pragma unroll
+            for (int e = 0; e < V; ++e) a[e] = 0.f;
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) {
+                if (i < n) {
+                    float xv[V];
+                    load_vec<V>(xs + i * C + v * V, xv);
+#pragma unroll
+                    for (int e = 0; e < V; ++e) a[e] = fmaf(hpv[i], xv[e], a[e]);
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < V; ++e) ss = fmaf(a[e], a[e], ss);
+        }
+        return ss;
+    };
 
     if constexpr (DYN) {
         // 1a. sum the split partial results of this token
@@ -175,8 +203,25 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
         if (tid == 0) p.rms_h[b] = (float)r;
         __syncthreads();
         MHC_STAMP();
-        // 1c. Sinkhorn-Knopp in the registers of one thread
-        if (tid == 0) {
+        // 1c. Sinkhorn-Knopp: sixteen lanes of warp 0 for fp32 and n <= 4 (a step is two shuffles
+        //     and three arithmetic instructions), else in the registers of one thread
+        constexpr bool kLanes = std::is_same<A, float>::value && MAXN == 4;
+        if (kLanes && tid < 32) {
+            if constexpr (kLanes) {
+                const int e = tid & 15, i = e >> 2, j = e & 3;
+                const bool in = i < n && j < n;
+                float mv = in ? cfc[2 * MAXN + i * MAXN + j] : 0.f;
+                float* dn = p.sk_den != nullptr ? p.sk_den + b * 2 * (int64_t)p.iters * MAXN : nullptr;
+                if (dn != nullptr)
+                    mv = sk_forward_lanes4<true>(mv, e, n, p.iters, p.eps, dn, tid < 16);
+                else
+                    mv = sk_forward_lanes4<false>(mv, e, n, p.iters, p.eps, nullptr, false);
+                if (in && tid < 16) {
+                    cfc[2 * MAXN + i * MAXN + j] = mv;
+                    p.M[b * n * n + i * n + j] = mv;
+                }
+            }
+        } else if (!kLanes && tid == 0) {
             A m[MAXN][MAXN];
 #pragma unroll
             for (int i = 0; i < MAXN; ++i)
@@ -201,6 +246,22 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
                         p.M[b * n * n + i * n + j] = (float)m[i][j];
                     }
         }
+        // ... while the other warp waits for the row block and makes pass 1 over it (the sum of
+        // squares of the aggregated stream needs H_pre only), so that pass 1 costs no time of its
+        // own: the Sinkhorn thread is a chain of dependent instructions several thousand cycles long
+        if (tid >= 32) {
+            float hp1[MAXN];
+#pragma unroll
+            for (int i = 0; i < MAXN; ++i) hp1[i] = (i < n) ? cfc[i] : 0.f;
+            float ss1 = 0.f;
+            if (mbar_wait_bounded(bar, 0)) {
+                ss1 = pass1(tid - 32, kMixThreads - 32, hp1);
+            } else if (tid == 32) {
+                red[2] = 1.f;   // the copy did not land: reported after the barrier below
+            }
+            ss1 = warp_sum(ss1);
+            if ((tid & 31) == 0) red[tid >> 5] = ss1;
+        }
         __syncthreads();
     } else {
         for (int k = tid; k < n; k += kMixThreads) {
@@ -222,38 +283,30 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
         for (int j = 0; j < MAXN; ++j) m[i][j] = (i < n && j < n) ? cfc[2 * MAXN + i * MAXN + j] : 0.f;
     }
 
-    // 2. the row block has to have landed; the vote keeps the decision uniform over the block
-    const int ok = __syncthreads_and(mbar_wait_bounded(bar, 0) ? 1 : 0);
-    if (!ok) {
-        if (tid == 0 && p.status != nullptr) atomicOr(p.status, kDevErrBulkWait);
-        return;
-    }
-
-    MHC_STAMP();
-    const int64_t nvec = C / V;
-    // 3. pass 1: sum of squares of the aggregated stream
-    float ss = 0.f;
-#pragma unroll 2
-    for (int64_t v = tid; v < nvec; v += kMixThreads) {
-        float a[V];
-#pragma unroll
-        for (int e = 0; e < V; ++e) a[e] = 0.f;
-#pragma unroll
-        for (int i = 0; i < MAXN; ++i) {
-            if (i < n) {
-                float xv[V];
-                load_vec<V>(xs + i * C + v * V, xv);
-#pragma unroll
-                for (int e = 0; e < V; ++e) a[e] = fmaf(hp[i], xv[e], a[e]);
-            }
+    // 2. the row block has to have landed; the decision is uniform over the block
+    float tot;
+    if constexpr (DYN) {
+        // warp 1 waited and made pass 1 during the Sinkhorn iterations (barrier above)
+        if (red[2] != 0.f || !mbar_wait_bounded(bar, 0)) {
+            if (tid == 0 && p.status != nullptr) atomicOr(p.status, kDevErrBulkWait);
+            return;
         }
-#pragma unroll
-        for (int e = 0; e < V; ++e) ss = fmaf(a[e], a[e], ss);
+        MHC_STAMP();
+        tot = red[1];
+    } else {
+        const int ok = __syncthreads_and(mbar_wait_bounded(bar, 0) ? 1 : 0);
+        if (!ok) {
+            if (tid == 0 && p.status != nullptr) atomicOr(p.status, kDevErrBulkWait);
+            return;
+        }
+        MHC_STAMP();
+        // 3. pass 1: sum of squares of the aggregated stream
+        float ss = pass1(tid, kMixThreads, hp);
+        ss = warp_sum(ss);
+        if ((tid & 31) == 0) red[tid >> 5] = ss;
+        __syncthreads();
+        tot = red[0] + red[1];
     }
-    ss = warp_sum(ss);
-    if ((tid & 31) == 0) red[tid >> 5] = ss;
-    __syncthreads();
-    const float tot = red[0] + red[1];
     const float rho = sqrtf(tot / (float)C + p.eps);
     const float ri = 1.f / rho;
     if (tid == 0) p.rho[b] = rho;

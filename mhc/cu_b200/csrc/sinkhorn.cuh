@@ -123,6 +123,35 @@ __device__ __forceinline__ float sk_rcp<float>(float v) {
 template <>
 __device__ __forceinline__ double sk_rcp<double>(double v) { return 1.0 / v; }
 
+// Forward sweep with SIXTEEN LANES PER MATRIX (n <= 4, fp32): lane e holds m[i][j] with
+// (i, j) = (e >> 2, e & 3); entries outside the n x n matrix must be 0.  Row sums are two xor
+// shuffles (1, 2), column sums two more (4, 8).  den (optional, [2*iters][4] of this matrix, same
+// layout as sk_forward_thread with MAXN = 4): row denominators are stored by the lanes j == 0,
+// column denominators by the lanes i == 0.  All 32 lanes of a warp must call this together (the
+// upper half-warp may hold a second matrix or a copy); `store` says whether this lane may write.
+template <bool STORE>
+__device__ __forceinline__ float sk_forward_lanes4(float m, int e, int n, int iters, float eps,
+                                                   float* den, bool store) {
+    const int i = e >> 2, j = e & 3;
+    const bool in = store && i < n && j < n;
+    for (int t = 0; t < iters; ++t) {
+        float rs = m;
+        rs += __shfl_xor_sync(0xffffffffu, rs, 1);
+        rs += __shfl_xor_sync(0xffffffffu, rs, 2);
+        const float rd = rs + eps;
+        m *= sk_rcp<float>(rd);
+        if (STORE && in && j == 0) den[(2 * t) * 4 + i] = rd;
+        float cs = m;
+        cs += __shfl_xor_sync(0xffffffffu, cs, 4);
+        cs += __shfl_xor_sync(0xffffffffu, cs, 8);
+        const float cd = cs + eps;
+        m *= sk_rcp<float>(cd);
+        if (STORE && in && i == 0) den[(2 * t + 1) * 4 + j] = cd;
+    }
+    return m;
+}
+
+
 // den (optional), element stride ds: den[((2t) * MAXN + i) * ds] = row sum + eps of row i at
 // iteration t, den[((2t+1) * MAXN + j) * ds] = column sum + eps of column j.
 template <int MAXN, typename A, bool STORE>
