@@ -69,4 +69,14 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gm
         : "memory");
 }
 
+// the same with an L2 eviction-priority policy (createpolicy) for the lines it reads
+__device__ __forceinline__ void bulk_copy_g2s_hint(void* dst_smem, const void* src_gmem,
+                                                   uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;"
+        ::"r"(smem_addr(dst_smem)), "l"(src_gmem), "r"(bytes), "r"(smem_addr(bar)), "l"(policy)
+        : "memory");
+}
+
 }  // namespace mhc

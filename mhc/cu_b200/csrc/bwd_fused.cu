@@ -23,6 +23,7 @@
 // dynamic backward (src/python/mhc/ops.py:330-349) and its stream_distribute_mix_backward /
 // stream_aggregate_backward / rmsnorm_backward kernels (src/csrc/kernels/stream_ops.cuh:644-997,
 // src/csrc/kernels/rmsnorm.cuh:233-306).
+#include "cache_hint.cuh"
 #include "kernels.h"
 
 namespace mhc {
@@ -54,6 +55,14 @@ __device__ __forceinline__ void f_cp_async16(void* dst_smem, const void* src, ui
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
                      (uint32_t)__cvta_generic_to_shared(dst_smem)),
                  "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+// the same with an L2 eviction-priority policy for the line it reads
+__device__ __forceinline__ void f_cp_async16_hint(void* dst_smem, const void* src, uint32_t src_bytes,
+                                                  uint64_t policy) {
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst_smem)),
+                 "l"(src), "r"(src_bytes), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ void f_cp_async_commit() {
@@ -171,6 +180,7 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
         src_off[u] = (int64_t)t * nC + (int64_t)j * C + (chunk_col_in[u] ? c0 + 8 * part : 0);
         dst_off[u] = t * TOKB + j * (kFCols * 2) + part * 16;
     }
+    const uint64_t last_use = l2_evict_first();   // this pass is the last reader of x and dy; dx is write-only
     const bool has_rec = tid < kFTok * (RS / 4);
     const int rec_tok = tid / (RS / 4), rec_part = tid % (RS / 4);
     auto prefetch = [&](int64_t grp, int buf) {
@@ -181,8 +191,8 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
             if (chunk_tok[u] >= 0) {
                 const bool in = (t0 + chunk_tok[u] < B) && chunk_col_in[u];
                 const int64_t off = in ? t0 * nC + src_off[u] : 0;
-                f_cp_async16(base + dst_off[u], x + off, in ? 16u : 0u);
-                f_cp_async16(base + dst_off[u] + TILEB, gy + off, in ? 16u : 0u);
+                f_cp_async16_hint(base + dst_off[u], x + off, in ? 16u : 0u, last_use);
+                f_cp_async16_hint(base + dst_off[u] + TILEB, gy + off, in ? 16u : 0u, last_use);
             }
         }
         if (has_rec) {
@@ -331,8 +341,8 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
 #pragma unroll
             for (int u = 0; u < PER_THREAD; ++u) {
                 if (chunk_tok[u] >= 0 && (t0 + chunk_tok[u] < B) && chunk_col_in[u])
-                    *reinterpret_cast<uint4*>(dx + t0 * nC + src_off[u]) =
-                        *reinterpret_cast<const uint4*>(xs + dst_off[u]);
+                    stg_hint(dx + t0 * nC + src_off[u],
+                             *reinterpret_cast<const uint4*>(xs + dst_off[u]), last_use);
             }
         }
         __syncthreads();   // the stage may be overwritten by the prefetch of the next iteration

@@ -28,6 +28,7 @@
 // per-token coefficients.
 #include <cuda_bf16.h>
 
+#include "cache_hint.cuh"
 #include "coeffs_lanes.cuh"
 #include "kernels.h"
 
@@ -45,14 +46,6 @@ __device__ __forceinline__ void g_mma_16816(float (&c)[4], uint32_t a0, uint32_t
         "{%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint4 g_ldg_stream(const bf16* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
 }
 
 __device__ __forceinline__ uint32_t g_mul_bf16x2(uint32_t a, uint32_t b) {
@@ -127,6 +120,7 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
     // of loads covers whole 128-byte lines of its eight rows
     const int nchunk = (int)(C / 64);
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint64_t keep = l2_evict_last();   // x and dy are read once more, by the dx pass
     for (int c0 = warp; c0 < nchunk; c0 += kGWarps * kGBatch) {
         uint4 gv[kGBatch][2], xv[kGBatch][2];
 #pragma unroll
@@ -136,8 +130,8 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
             const int64_t off = (int64_t)c * 64 + 16 * q;
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                gv[u][e] = in ? g_ldg_stream(gr + off + 8 * e) : zero;
-                xv[u][e] = in ? g_ldg_stream(xr + off + 8 * e) : zero;
+                gv[u][e] = in ? ldg_stream_hint(gr + off + 8 * e, keep) : zero;
+                xv[u][e] = in ? ldg_stream_hint(xr + off + 8 * e, keep) : zero;
             }
         }
 #pragma unroll

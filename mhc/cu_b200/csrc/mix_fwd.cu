@@ -19,6 +19,7 @@
 #include <type_traits>
 
 #include "async.cuh"
+#include "cache_hint.cuh"
 #include "kernels.h"
 #include "sinkhorn.cuh"
 
@@ -101,7 +102,7 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
     // they have arrived (it then lands while the Sinkhorn thread works).
     if (!DYN && tid == 0) {
         mbar_arrive_expect_tx(bar, row_bytes);
-        bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
+        bulk_copy_g2s_hint(xs, p.x + b * n * C, row_bytes, bar, l2_evict_last());
     }
     if (tid == 0) {
         red[0] = 0.f;
@@ -175,7 +176,7 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
         __syncthreads();
         if (tid == 0) {
             mbar_arrive_expect_tx(bar, row_bytes);
-            bulk_copy_g2s(xs, p.x + b * n * C, row_bytes, bar);
+            bulk_copy_g2s_hint(xs, p.x + b * n * C, row_bytes, bar, l2_evict_last());
         }
         MHC_STAMP();
         // 1b. activations, one output per thread
@@ -314,6 +315,7 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
 
     // 4. pass 2: outputs
     T* yb = p.y + b * n * C;
+    const uint64_t ypol = l2_evict_first();
 #pragma unroll 2
     for (int64_t v = tid; v < nvec; v += kMixThreads) {
         float xv[MAXN][V], yn[V], wv[V];
@@ -345,7 +347,16 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
                     for (int j = 0; j < MAXN; ++j) t = fmaf(m[i][j], xv[j][e], t);
                     o[e] = t;
                 }
-                store_vec<V>(yb + i * C + v * V, o);
+                if constexpr (std::is_same<T, bf16>::value && V == 8) {
+                    uint4 t4;
+                    t4.x = pack_bf16x2(o[0], o[1]);
+                    t4.y = pack_bf16x2(o[2], o[3]);
+                    t4.z = pack_bf16x2(o[4], o[5]);
+                    t4.w = pack_bf16x2(o[6], o[7]);
+                    stg_hint(yb + i * C + v * V, t4, ypol);   // y is not read again by this layer
+                } else {
+                    store_vec<V>(yb + i * C + v * V, o);
+                }
             }
         }
     }

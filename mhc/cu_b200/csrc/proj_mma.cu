@@ -20,6 +20,7 @@
 //
 // Takes over compute_rms + the cuBLASLt bf16 GEMM of the reference
 // (src/csrc/kernels/fused_rmsnorm_matmul.cuh:15-153, src/python/bindings.cu:21-111,426-443).
+#include "cache_hint.cuh"
 #include "kernels.h"
 
 namespace mhc {
@@ -47,15 +48,6 @@ __device__ __forceinline__ float sumsq8(const uint4& v) {
     t = bf16_lo(v.z); s = fmaf(t, t, s); t = bf16_hi(v.z); s = fmaf(t, t, s);
     t = bf16_lo(v.w); s = fmaf(t, t, s); t = bf16_hi(v.w); s = fmaf(t, t, s);
     return s;
-}
-
-// streaming 16-byte load that leaves L1 to phi
-__device__ __forceinline__ uint4 ldg_stream(const bf16* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
 }
 
 // NT = output tiles of 8 handled by one block (blockIdx.z picks the group of NT tiles);
@@ -92,6 +84,7 @@ proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
         for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
     float sslo = 0.f, sshi = 0.f;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const uint64_t keep = l2_evict_last();   // x is read again by the kernels that follow
 
     // A batch is kCH * 32 = 128 reduction elements, walked as two 64-element pieces: the four
     // lanes of a row take 32 contiguous bytes each (two 16-byte loads), so that a warp's loads
@@ -104,8 +97,8 @@ proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
         for (int c = 0; c < kCH; ++c) {
             const int64_t k = kb + (c >> 1) * 64 + 16 * q + 8 * (c & 1);
             const bool in = k < nC;  // nC is a multiple of 8, so a started vector is a whole vector
-            r[c] = (in && vlo) ? ldg_stream(xlo + k) : zero;
-            s[c] = (in && vhi) ? ldg_stream(xhi + k) : zero;
+            r[c] = (in && vlo) ? ldg_stream_hint(xlo + k, keep) : zero;
+            s[c] = (in && vhi) ? ldg_stream_hint(xhi + k, keep) : zero;
         }
 #pragma unroll
         for (int c = 0; c < kCH; ++c) {
