@@ -24,6 +24,7 @@
 // stream_aggregate_backward / rmsnorm_backward kernels (src/csrc/kernels/stream_ops.cuh:644-997,
 // src/csrc/kernels/rmsnorm.cuh:233-306).
 #include "cache_hint.cuh"
+#include "launch.cuh"
 #include "kernels.h"
 
 namespace mhc {
@@ -111,6 +112,7 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
                   RECB = Cfg::RECB, DPB = Cfg::DPB, STAGES = Cfg::STAGES;
     extern __shared__ __align__(128) unsigned char smem[];
 
+    pdl_trigger();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, q = lane & 3;
     const int64_t c0 = (int64_t)blockIdx.x * kFCols;
@@ -217,6 +219,9 @@ dx_dphi_kernel(bf16* __restrict__ dx, float* __restrict__ dphi_part, float* __re
     };
 
     static_assert(kFTok * (KP / 8) + KP * 2 <= kFWarps * 32, "A-operand chunks exceed the block");
+    // phi and w above are inputs of the call; the records and dp operands below come from the
+    // kernel before this one
+    pdl_wait();
     int buf = 0;
 #pragma unroll
     for (int u = 0; u < STAGES - 1; ++u)
@@ -419,8 +424,9 @@ cudaError_t launch_dx_dphi_fused(bf16* dx, float* dphi, float* dphi_part, float*
     cudaError_t e = cudaFuncSetAttribute(dx_dphi_kernel<4>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    dx_dphi_kernel<4><<<grid, kFWarps * 32, smem, s>>>(dx, part, dw_part, x, g, w, rec, dprb, dprT,
-                                                        phi, d.B, Bp, d.C, gpb);
+    e = launch_chain(dx_dphi_kernel<4>, grid, dim3(kFWarps * 32), smem, s, true, dx, part, dw_part, x,
+                     g, w, rec, dprb, dprT, phi, d.B, Bp, d.C, gpb);
+    if (e != cudaSuccess) return e;
     return launched();
 }
 

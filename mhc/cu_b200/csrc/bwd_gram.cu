@@ -29,6 +29,7 @@
 #include <cuda_bf16.h>
 
 #include "cache_hint.cuh"
+#include "launch.cuh"
 #include "coeffs_lanes.cuh"
 #include "kernels.h"
 
@@ -70,6 +71,7 @@ bwd_gram_kernel(float* __restrict__ dH, float* __restrict__ c2out, const bf16* _
     __shared__ float c2s[2];
     __shared__ float pts[2][28];                // FUSE: the tokens' terms of d_bias and d_alpha
     extern __shared__ __align__(16) float den[];   // FUSE: [2 tokens][2*iters][4] saved denominators
+    pdl_trigger();   // the dx pass that follows may fetch its phi fragments while this kernel drains
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gq = lane >> 2, q = lane & 3;     // fragment row / column group
     const int64_t pair = blockIdx.x;

@@ -20,6 +20,7 @@
 
 #include "async.cuh"
 #include "cache_hint.cuh"
+#include "launch.cuh"
 #include "kernels.h"
 #include "sinkhorn.cuh"
 
@@ -92,18 +93,16 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
 #endif
     MHC_STAMP();
 
+    pdl_trigger();
     if (tid == 0) {
         mbar_init(bar, 1);
         mbar_init_fence();
-    }
-    // Static coefficients: the row copy starts at once.  Dynamic: every block of the single wave
-    // starts together, and small loads issued behind 26 MB of row copies wait for them; so the
-    // partial results, alpha and the biases are fetched first and the row copy is issued when
-    // they have arrived (it then lands while the Sinkhorn thread works).
-    if (!DYN && tid == 0) {
+        // x is an input of the call, not a product of the kernel before this one: the row copy
+        // starts before the wait below and flies while the projection kernel drains
         mbar_arrive_expect_tx(bar, row_bytes);
         bulk_copy_g2s_hint(xs, p.x + b * n * C, row_bytes, bar, l2_evict_last());
     }
+    pdl_wait();   // partial projections (dynamic) / coefficients (static) come from the predecessor
     if (tid == 0) {
         red[0] = 0.f;
         red[2] = 0.f;   // "row copy failed" flag of the dynamic path
@@ -174,10 +173,6 @@ mix_fwd_kernel(const MixFwdParams<T> p) {
         const float al0 = p.alpha[0], al1 = p.alpha[1], al2 = p.alpha[2];
         const float bias_k = (tid < K) ? p.bias[tid] : 0.f;
         __syncthreads();
-        if (tid == 0) {
-            mbar_arrive_expect_tx(bar, row_bytes);
-            bulk_copy_g2s_hint(xs, p.x + b * n * C, row_bytes, bar, l2_evict_last());
-        }
         MHC_STAMP();
         // 1b. activations, one output per thread
         const A r = mix_sqrt<A>(A(cf[K]) / A(n * C) + A(p.eps));
@@ -409,12 +404,14 @@ static cudaError_t mix_fwd_launch(const MixFwdParams<T>& p, Dims d, bool use_dou
         auto k = mix_fwd_kernel<T, V, MAXN, DYN, double>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         if (e != cudaSuccess) return e;
-        k<<<grid, kMixThreads, smem, s>>>(p);
+        e = launch_chain(k, dim3(grid), dim3(kMixThreads), smem, s, true, p);
+        if (e != cudaSuccess) return e;
     } else {
         auto k = mix_fwd_kernel<T, V, MAXN, DYN, float>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
         if (e != cudaSuccess) return e;
-        k<<<grid, kMixThreads, smem, s>>>(p);
+        e = launch_chain(k, dim3(grid), dim3(kMixThreads), smem, s, true, p);
+        if (e != cudaSuccess) return e;
     }
     return launched();
 }

@@ -21,6 +21,7 @@
 // Takes over compute_rms + the cuBLASLt bf16 GEMM of the reference
 // (src/csrc/kernels/fused_rmsnorm_matmul.cuh:15-153, src/python/bindings.cu:21-111,426-443).
 #include "cache_hint.cuh"
+#include "launch.cuh"
 #include "kernels.h"
 
 namespace mhc {
@@ -57,6 +58,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 proj_mma_kernel(float* __restrict__ praw_part, float* __restrict__ sumsq_part,
                 const bf16* __restrict__ x, const bf16* __restrict__ phi, int64_t B, int K,
                 int64_t nC, int nb) {
+    pdl_trigger();   // the fused forward that follows may start its row copies while this kernel drains
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const int64_t t0 = ((int64_t)blockIdx.x * kWarps + warp) * kTokens;

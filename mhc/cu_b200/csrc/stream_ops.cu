@@ -14,6 +14,7 @@
 // per-token coefficients in the backward, which the reference's dynamic path lacks
 // (it indexes M / H_post / H_pre without a batch offset, stream_ops.cuh:767-770).
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace mhc {
 
@@ -347,6 +348,7 @@ __global__ void finalize_kernel(float* __restrict__ d_w, const float* __restrict
                                 int nparts, int64_t C, float* __restrict__ d_bias,
                                 float* __restrict__ d_alpha, const float* __restrict__ partials,
                                 int nparts2, int K, DphiSum ds) {
+    pdl_wait();   // everything read here was written by the kernels before this one
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < ds.total4) {
         float4 t = reinterpret_cast<const float4*>(ds.part)[i];
@@ -491,8 +493,9 @@ cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_
     int64_t items = C > (int64_t)(K + 3) * 32 ? C : (int64_t)(K + 3) * 32;
     if (ds.total4 > items) items = ds.total4;
     const unsigned grid = (unsigned)((items + 255) / 256);
-    finalize_kernel<<<grid, 256, 0, s>>>(d_w, dw_part, nparts, C, d_bias, d_alpha, partials, nparts2,
-                                         K, ds);
+    const cudaError_t e = launch_chain(finalize_kernel, dim3(grid), dim3(256), 0, s, true, d_w, dw_part,
+                                       nparts, C, d_bias, d_alpha, partials, nparts2, K, ds);
+    if (e != cudaSuccess) return e;
     return launched();
 }
 
