@@ -7,7 +7,8 @@ One step = one forward + backward of the dynamic-H mHC layer over one batch of s
 tokens (default workload c3: x [1280, 4, 2560] bf16 per GPU, phi ~ N(0, 0.02), alpha 0.01, eps 1e-6,
 20 Sinkhorn iterations).  With N > 1 (launched by torchrun, one rank per GPU) every rank works on
 its own batch of the same size (weak scaling) and the flat fp32 parameter-gradient bucket is
-all-reduced with NCCL inside the step.  Rank 0 prints ONE JSON line.
+all-reduced with NCCL on a second stream, overlapping the next step (two alternating buckets);
+every all-reduce completes inside the timed region.  Rank 0 prints ONE JSON line.
 
   value      tokens/s over all ranks, inputs resident in HBM, K steps timed with CUDA events between
              barrier+synchronize pairs, max over ranks.  Steps rotate over several input sets so the
@@ -221,6 +222,10 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # The collective is 1 MB and runs (on a high-priority stream) next to kernels that are sized
+        # as one resident wave over all SMs: a handful of NCCL blocks is enough to finish it within
+        # a step (measured on two GPUs: 1 block 215 us per step, 2: 113, 6 to 32: 75).
+        os.environ.setdefault("NCCL_MAX_CTAS", "8")
         dist.init_process_group("nccl", device_id=dev)
     lib = L.lib()
 
@@ -246,11 +251,10 @@ def main():
                       "M": torch.empty(B, n, n, **f32), "proj": torch.empty(B, K, **f32),
                       "sk_den": torch.empty(B, 2 * iters, 4 if n <= 4 else 8, **f32)})
     # flat gradient bucket the backward writes into and the ranks all-reduce
+    # With more than one rank there are two buckets, used by alternating input sets: while one is
+    # being all-reduced on the communication stream the next step writes the other.
     from mhc.cu_b200.distributed import GradBucket
-    bucket_obj = GradBucket(n, C, dev)
-    bucket = bucket_obj.flat
-    d_phi, d_bias, d_alpha, d_w = (bucket_obj.d_phi, bucket_obj.d_bias, bucket_obj.d_alpha,
-                                   bucket_obj.d_rmsnorm_weight)
+    buckets = [GradBucket(n, C, dev) for _ in range(2 if world > 1 else 1)]
     ws_f = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag) + 16,
                        dtype=torch.uint8, device=dev)
     ws_b = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_BWD, B, n, C, iters, tag) + 16,
@@ -258,6 +262,8 @@ def main():
 
     def launch_step(r, stream):
         s = saved[r]
+        bk = buckets[r % len(buckets)]
+        d_phi, d_bias, d_alpha, d_w = bk.d_phi, bk.d_bias, bk.d_alpha, bk.d_rmsnorm_weight
         st = lib.mhc_dynamic_fwd(
             ys[r].data_ptr(), s["rms"].data_ptr(), s["rms_h"].data_ptr(), s["H_pre"].data_ptr(),
             s["H_post"].data_ptr(), s["M"].data_ptr(), s["proj"].data_ptr(), s["sk_den"].data_ptr(),
@@ -272,10 +278,39 @@ def main():
             B, n, C, iters, eps, tag, ws_b.data_ptr(), ws_b.numel(), stream)
         L.check(st, "mhc_dynamic_bwd")
 
-    def reduce_grads():
-        # the one collective of the step: the flat fp32 parameter-gradient bucket
+    comm = torch.cuda.Stream(priority=-1) if world > 1 else None
+    ready = [torch.cuda.Event() for _ in buckets]      # the step that filled the bucket is done
+    reduced = [torch.cuda.Event() for _ in buckets]    # its all-reduce is done
+    in_flight = [False for _ in buckets]
+
+    def reduce_grads(r):
+        # the one collective of the step: the flat fp32 parameter-gradient bucket, all-reduced on
+        # the communication stream so that it overlaps the next step (as a data-parallel trainer
+        # overlaps it with the backward of the other layers)
         if world > 1:
-            dist.all_reduce(bucket)
+            b = r % len(buckets)
+            main = torch.cuda.current_stream()
+            ready[b].record(main)
+            comm.wait_event(ready[b])
+            with torch.cuda.stream(comm):
+                dist.all_reduce(buckets[b].flat)
+                reduced[b].record(comm)
+            in_flight[b] = True
+
+    def bucket_free(r):
+        # the step about to run overwrites bucket r % 2: its previous all-reduce has to be over
+        if world > 1:
+            b = r % len(buckets)
+            if in_flight[b]:
+                torch.cuda.current_stream().wait_event(reduced[b])
+                in_flight[b] = False
+
+    def drain():
+        if world > 1:
+            for b in range(len(buckets)):
+                if in_flight[b]:
+                    torch.cuda.current_stream().wait_event(reduced[b])
+                    in_flight[b] = False
 
     # kernels per step (counted by the library while one step is enqueued)
     mark("problem built")
@@ -283,7 +318,8 @@ def main():
     launch_step(0, torch.cuda.current_stream().cuda_stream)
     torch.cuda.synchronize()
     kernels_per_step = int(lib.mhc_kernels_enqueued() - k0)
-    reduce_grads()
+    reduce_grads(0)
+    drain()
     torch.cuda.synchronize()
     mark("first step and all-reduce done")
 
@@ -297,7 +333,7 @@ def main():
                 with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     launch_step(r, torch.cuda.current_stream().cuda_stream)
                 graphs.append(g)
-            graph_note = "cuda graph replay" + (" + eager all-reduce" if world > 1 else "")
+            graph_note = "cuda graph replay" + (" + all-reduce on a second stream" if world > 1 else "")
         except Exception as e:  # capture of the collective can be refused; fall back to eager
             graphs = None
             graph_note = f"python launches (graph capture failed: {type(e).__name__})"
@@ -307,11 +343,12 @@ def main():
 
     def step(i):
         r = i % R
+        bucket_free(r)
         if graphs is not None:
             graphs[r].replay()
         else:
             launch_step(r, torch.cuda.current_stream().cuda_stream)
-        reduce_grads()
+        reduce_grads(r)
 
     def barrier():
         if world > 1:
@@ -320,6 +357,7 @@ def main():
 
     for i in range(args.warmup):
         step(i)
+    drain()
     barrier()
     mark("warm-up done")
     sampler = ClockSampler(local_rank) if not args.profile else None
@@ -329,6 +367,7 @@ def main():
     e0.record()
     for i in range(args.steps):
         step(i)
+    drain()   # the last all-reduces are inside the timed region
     e1.record()
     barrier()
     mark("timed region done")
