@@ -466,9 +466,10 @@ def main():
                     "api": "mhc.MHCLayer forward + backward, pinned host buffers"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of the six kernels of one
-                         # c3 step, ncu capture summarised in profiles/bench_c3_step_kernels.md
-                         "traffic": 168.2e6 if args.workload == "c3" else None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of the five kernels of one
+                         # c3 step, each with cold caches (ncu capture summarised in
+                         # profiles/bench_c3_step_kernels.md)
+                         "traffic": 172.1e6 if args.workload == "c3" else None,
                          "peak_source": peak_kind,
                          "algorithmic_bytes_per_step": abytes,
                          "scope": "all kernels of one fwd+bwd step on one GPU"},
