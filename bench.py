@@ -196,6 +196,11 @@ def main():
     ap.add_argument("--sets", type=int, default=4, help="input sets rotated to exceed L2")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python every step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--strong", action="store_true",
+                    help="strong scaling: the workload's B tokens are split over the ranks")
+    ap.add_argument("--exposed-allreduce", action="store_true",
+                    help="issue the gradient all-reduce on the compute stream after every step "
+                         "instead of overlapping it with the next step")
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--profile", action="store_true",
                     help="kernel loop only (for ncu): no end-to-end leg, CPU baseline or clock sampling")
@@ -225,11 +230,16 @@ def main():
         # The collective is 1 MB and runs (on a high-priority stream) next to kernels that are sized
         # as one resident wave over all SMs: a handful of NCCL blocks is enough to finish it within
         # a step (measured on two GPUs: 1 block 215 us per step, 2: 113, 6 to 32: 75).
-        os.environ.setdefault("NCCL_MAX_CTAS", "8")
+        if not args.exposed_allreduce:
+            os.environ.setdefault("NCCL_MAX_CTAS", "8")
         dist.init_process_group("nccl", device_id=dev)
     lib = L.lib()
 
     B, n, C, dtype = cfg["B"], cfg["n"], cfg["C"], cfg["dtype"]
+    if args.strong and world > 1:
+        from mhc.cu_b200.distributed import shard_bounds
+        lo, hi = shard_bounds(B, rank, world)
+        B = hi - lo   # ranks may differ by one token; the slowest rank sets the time
     K = 2 * n + n * n
     iters, eps = cfg["iters"], cfg["eps"]
     tag = L.BF16 if dtype == torch.bfloat16 else L.F32
@@ -287,7 +297,9 @@ def main():
         # the one collective of the step: the flat fp32 parameter-gradient bucket, all-reduced on
         # the communication stream so that it overlaps the next step (as a data-parallel trainer
         # overlaps it with the backward of the other layers)
-        if world > 1:
+        if world > 1 and args.exposed_allreduce:
+            dist.all_reduce(buckets[r % len(buckets)].flat)
+        elif world > 1:
             b = r % len(buckets)
             main = torch.cuda.current_stream()
             ready[b].record(main)
@@ -333,7 +345,8 @@ def main():
                 with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     launch_step(r, torch.cuda.current_stream().cuda_stream)
                 graphs.append(g)
-            graph_note = "cuda graph replay" + (" + all-reduce on a second stream" if world > 1 else "")
+            graph_note = "cuda graph replay" + ((" + all-reduce after the step" if args.exposed_allreduce
+                                                 else " + all-reduce on a second stream") if world > 1 else "")
         except Exception as e:  # capture of the collective can be refused; fall back to eager
             graphs = None
             graph_note = f"python launches (graph capture failed: {type(e).__name__})"
@@ -392,7 +405,8 @@ def main():
     clocks = sampler.stop()
     mark("clock sampling done")
     ms_per_step = ms / args.steps
-    value = world * B * args.steps / (ms * 1e-3)
+    tokens_per_step = cfg["B"] if (args.strong and world > 1) else world * B
+    value = tokens_per_step * args.steps / (ms * 1e-3)
 
     # ---- end to end through the public API, host buffers in, results out --------------------
     import mhc
@@ -466,7 +480,7 @@ def main():
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
-    e2e_value = world * B * e2e_steps / (e2e_ms * 1e-3)
+    e2e_value = tokens_per_step * e2e_steps / (e2e_ms * 1e-3)
     h2d = 2 * B * n * C * io_bytes
     d2h = 2 * B * n * C * io_bytes + n_grad * 4
 
@@ -477,7 +491,8 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
+            "scaling": "strong" if args.strong else "weak", "vs_baseline": None,
+            "dtype": "bf16" if dtype == torch.bfloat16 else "f32",
             "data": "synthetic",
             "config": {"workload": args.workload, "kind": "dynamic-H fwd+bwd", "B_per_gpu": B, "n": n,
                        "C": C, "sinkhorn_iters": iters, "eps": eps, "parallelism": f"dp{world}",
