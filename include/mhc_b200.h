@@ -51,7 +51,8 @@ enum mhc_op {
     MHC_OP_SINKHORN_FWD = 4,
     MHC_OP_SINKHORN_BWD = 5,
     MHC_OP_RMSNORM_FWD = 6,
-    MHC_OP_RMSNORM_BWD = 7
+    MHC_OP_RMSNORM_BWD = 7,
+    MHC_OP_SINKHORN_RECT_BWD = 8   /* B = rows M, n = columns N of the single matrix */
 };
 
 /* Human-readable text for an mhc_status.  Never NULL.
@@ -155,6 +156,20 @@ int mhc_sinkhorn_fwd(float* out, const float* inp, int64_t batch, int n, int ite
 int mhc_sinkhorn_bwd(float* d_inp, const float* grad_out, const float* inp, int64_t batch, int n,
                      int iters, float eps, void* workspace, size_t workspace_bytes,
                      mhc_stream_t stream);
+
+/* Sinkhorn-Knopp on ONE rectangular fp32 matrix inp [M, N], 1 <= M, N <= 128 (row step, then
+ * column step, iters times, each division by sum + eps): the shape range of the reference's
+ * single-matrix op.  Replaces sinkhorn_knopp_fwd for 2-D inputs (src/python/bindings.cu:115-121,
+ * src/csrc/kernels/sinkhorn_knopp.cuh:423-459). */
+int mhc_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N, int iters, float eps,
+                          mhc_stream_t stream);
+
+/* Exact gradient of mhc_sinkhorn_rect_fwd w.r.t. inp for any M, N <= 128 (the reference's
+ * sinkhorn_knopp_bwd, src/python/bindings.cu:123-132, handles square matrices only).  Workspace:
+ * mhc_workspace_bytes(MHC_OP_SINKHORN_RECT_BWD, M, N, 0, iters, MHC_F32). */
+int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp, int M, int N,
+                          int iters, float eps, void* workspace, size_t workspace_bytes,
+                          mhc_stream_t stream);
 
 /* Same result as mhc_sinkhorn_bwd, for callers that cannot supply a workspace at all: a plug-in
  * inside a host that owns every byte of device memory and exposes no allocator, or a caller that

@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libmhc_b200.so")
 F32, BF16 = 0, 1
 OP_DYNAMIC_FWD, OP_DYNAMIC_BWD, OP_STATIC_FWD, OP_STATIC_BWD = 0, 1, 2, 3
 OP_SINKHORN_FWD, OP_SINKHORN_BWD, OP_RMSNORM_FWD, OP_RMSNORM_BWD = 4, 5, 6, 7
+OP_SINKHORN_RECT_BWD = 8
 
 _p, _i, _l, _f, _z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
@@ -30,6 +31,8 @@ SIGNATURES = {
     "mhc_static_bwd": (_i, [_p] * 13 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_sinkhorn_fwd": (_i, [_p, _p, _l, _i, _i, _f, _p]),
     "mhc_sinkhorn_bwd": (_i, [_p, _p, _p, _l, _i, _i, _f, _p, _z, _p]),
+    "mhc_sinkhorn_rect_fwd": (_i, [_p, _p, _i, _i, _i, _f, _p]),
+    "mhc_sinkhorn_rect_bwd": (_i, [_p, _p, _p, _i, _i, _i, _f, _p, _z, _p]),
     "mhc_sinkhorn_bwd_noalloc": (_i, [_p, _p, _p, _l, _i, _i, _f, _p]),
     "mhc_sinkhorn_bwd_noalloc_capacity": (_z, []),
     "mhc_rmsnorm_fwd": (_i, [_p, _p, _p, _p, _l, _l, _f, _p]),

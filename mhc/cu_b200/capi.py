@@ -194,11 +194,24 @@ def static_bwd(dy, x, rmsnorm_weight, H_res, saved, iters, eps, *, grads=None, d
     return dx, grads
 
 
+def _is_rect(inp):
+    """A single 2-D matrix that the batched square kernels (n <= 32) do not cover."""
+    return inp.dim() == 2 and (inp.shape[0] != inp.shape[1] or inp.shape[0] > 32)
+
+
 def sinkhorn_fwd(inp, iters, eps):
-    """mhc_sinkhorn_fwd on fp32 [n,n] or [batch,n,n]."""
+    """mhc_sinkhorn_fwd on fp32 [n,n] / [batch,n,n] (n <= 32), mhc_sinkhorn_rect_fwd on one [M,N]
+    matrix with M, N <= 128."""
     _chk(inp, "inp", torch.float32)
+    if _is_rect(inp):
+        M, N = inp.shape
+        out = _empty_like(inp)
+        st = L.lib().mhc_sinkhorn_rect_fwd(_ptr(out), _ptr(inp), M, N, int(iters), float(eps),
+                                           _stream())
+        L.check(st, "mhc_sinkhorn_rect_fwd")
+        return out
     if inp.dim() not in (2, 3) or inp.shape[-1] != inp.shape[-2]:
-        raise ValueError("sinkhorn expects [n,n] or [batch,n,n] square matrices")
+        raise ValueError("sinkhorn expects one [M,N] matrix (M, N <= 128) or square [batch,n,n]")
     n = inp.shape[-1]
     batch = inp.shape[0] if inp.dim() == 3 else 1
     out = _empty_like(inp)
@@ -211,6 +224,15 @@ def sinkhorn_bwd(grad_out, inp, iters, eps):
     """mhc_sinkhorn_bwd: gradient w.r.t. ``inp`` of sinkhorn_fwd(inp)."""
     _chk(inp, "inp", torch.float32)
     _chk(grad_out, "grad_out", torch.float32, inp.shape)
+    if _is_rect(inp):
+        M, N = inp.shape
+        d_inp = _empty_like(inp)
+        nbytes = workspace_bytes(L.OP_SINKHORN_RECT_BWD, M, N, 0, iters, L.F32)
+        ws = _workspace(nbytes, inp.device)
+        st = L.lib().mhc_sinkhorn_rect_bwd(_ptr(d_inp), _ptr(grad_out), _ptr(inp), M, N, int(iters),
+                                           float(eps), _ptr(ws), ws.numel(), _stream())
+        L.check(st, "mhc_sinkhorn_rect_bwd")
+        return d_inp
     n = inp.shape[-1]
     batch = inp.shape[0] if inp.dim() == 3 else 1
     d_inp = _empty_like(inp)

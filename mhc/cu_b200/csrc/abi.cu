@@ -339,6 +339,10 @@ size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int d
         if (op == MHC_OP_RMSNORM_FWD) return 0;
         return (size_t)rmsnorm_bwd_blocks(B) * (size_t)C * sizeof(float) + 256;
     }
+    if (op == MHC_OP_SINKHORN_RECT_BWD) {
+        if (B < 1 || B > 128 || n < 1 || n > 128 || iters < 0) return (size_t)-1;
+        return sinkhorn_rect_bwd_ws(iters) + 256;
+    }
     if (check_dims(B, n, sk ? 1 : C, iters, sk ? MHC_F32 : dtype) != MHC_OK) return (size_t)-1;
     const Dims d{B, n, sk ? 1 : C};
     Carver c(nullptr);
@@ -483,6 +487,28 @@ int mhc_sinkhorn_bwd(float* d_inp, const float* grad_out, const float* inp, int6
     if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
     MHC_TRY(launch_sinkhorn_bwd(d_inp, grad_out, inp, workspace, batch, n, iters, eps,
                                 reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N, int iters, float eps,
+                          mhc_stream_t stream) {
+    if (M < 1 || N < 1 || M > 128 || N > 128 || iters < 0) return MHC_ERR_BAD_SHAPE;
+    if (!out || !inp) return MHC_ERR_NULL_POINTER;
+    MHC_TRY(launch_sinkhorn_rect_fwd(out, inp, M, N, iters, eps,
+                                     reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp, int M, int N,
+                          int iters, float eps, void* workspace, size_t workspace_bytes,
+                          mhc_stream_t stream) {
+    if (M < 1 || N < 1 || M > 128 || N > 128 || iters < 0) return MHC_ERR_BAD_SHAPE;
+    if (!d_inp || !grad_out || !inp) return MHC_ERR_NULL_POINTER;
+    if (!aligned16(workspace)) return MHC_ERR_MISALIGNED;
+    const size_t need = sinkhorn_rect_bwd_ws(iters);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    MHC_TRY(launch_sinkhorn_rect_bwd(d_inp, grad_out, inp, workspace, M, N, iters, eps,
+                                     reinterpret_cast<cudaStream_t>(stream)));
     return MHC_OK;
 }
 

@@ -155,6 +155,13 @@ cudaError_t launch_mix_fwd_static(T* y, float* rho, const T* x, const bf16* w, c
                                   const float* H_post, const float* M, int* status, Dims d,
                                   float eps, cudaStream_t s);
 
+// ---- sinkhorn_rect.cu: Sinkhorn-Knopp on one rectangular matrix, M, N <= 128 ------------------
+size_t sinkhorn_rect_bwd_ws(int iters);
+cudaError_t launch_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N, int iters,
+                                     float eps, cudaStream_t s);
+cudaError_t launch_sinkhorn_rect_bwd(float* d_inp, const float* grad, const float* inp, void* ws,
+                                     int M, int N, int iters, float eps, cudaStream_t s);
+
 // ---- bwd_gram.cu: backward pass A from tensor-core Gram matrices (bf16, n = 4) --------------
 bool bwd_gram_supported(Dims d);
 int bwd_gram_blocks(Dims d);   // rows of `partials` the fused variant writes

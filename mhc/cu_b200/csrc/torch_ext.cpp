@@ -40,13 +40,23 @@ Tensor workspace(int op, int64_t B, int n, int64_t C, int iters, int tag, const 
 }
 
 // ---- stand-alone ops -----------------------------------------------------------------------
+static bool is_rect(const Tensor& inp) {
+    return inp.dim() == 2 && (inp.size(0) != inp.size(1) || inp.size(0) > 32);
+}
+
 Tensor sinkhorn_knopp_fwd(Tensor inp, int64_t iters, double eps) {
     need(inp, "inp");
-    TORCH_CHECK(inp.scalar_type() == torch::kFloat32 && (inp.dim() == 2 || inp.dim() == 3) &&
-                    inp.size(-1) == inp.size(-2),
-                "sinkhorn expects fp32 [n,n] or [batch,n,n]");
+    TORCH_CHECK(inp.scalar_type() == torch::kFloat32 && (inp.dim() == 2 || inp.dim() == 3),
+                "sinkhorn expects fp32 [M,N] or [batch,n,n]");
     c10::cuda::CUDAGuard guard(inp.device());
     auto out = torch::empty_like(inp);
+    if (is_rect(inp)) {   // one matrix the batched square kernels do not cover (M, N <= 128)
+        check(mhc_sinkhorn_rect_fwd(out.data_ptr<float>(), inp.data_ptr<float>(), (int)inp.size(0),
+                                    (int)inp.size(1), (int)iters, (float)eps, stream()),
+              "mhc_sinkhorn_rect_fwd");
+        return out;
+    }
+    TORCH_CHECK(inp.size(-1) == inp.size(-2), "batched sinkhorn expects square matrices");
     const int64_t batch = inp.dim() == 3 ? inp.size(0) : 1;
     check(mhc_sinkhorn_fwd(out.data_ptr<float>(), inp.data_ptr<float>(), batch, (int)inp.size(-1),
                            (int)iters, (float)eps, stream()),
@@ -58,6 +68,16 @@ Tensor sinkhorn_knopp_bwd(Tensor grad, Tensor inp, int64_t iters, double eps) {
     need(grad, "grad");
     need(inp, "inp");
     c10::cuda::CUDAGuard guard(inp.device());
+    if (is_rect(inp)) {
+        auto d_rect = torch::empty_like(inp);
+        auto wsr = workspace(MHC_OP_SINKHORN_RECT_BWD, inp.size(0), (int)inp.size(1), 0, (int)iters,
+                             MHC_F32, inp);
+        check(mhc_sinkhorn_rect_bwd(d_rect.data_ptr<float>(), grad.data_ptr<float>(),
+                                    inp.data_ptr<float>(), (int)inp.size(0), (int)inp.size(1),
+                                    (int)iters, (float)eps, wsr.data_ptr(), wsr.numel(), stream()),
+              "mhc_sinkhorn_rect_bwd");
+        return d_rect;
+    }
     const int64_t batch = inp.dim() == 3 ? inp.size(0) : 1;
     const int n = (int)inp.size(-1);
     auto d_inp = torch::empty_like(inp);

@@ -38,3 +38,14 @@ def test_sinkhorn_backward_fp32_reconstruction_error():
     d64 = oracle.sinkhorn_backward(dM, E, 20, 1e-6)
     d32 = oracle.sinkhorn_backward(dM.float(), E.float(), 20, 1e-6)
     assert_rel(d32, d64, 2e-5, "fp32 sinkhorn backward")
+
+
+def test_sinkhorn_backward_rectangular_matches_autograd():
+    """The closed-form Sinkhorn backward on a single rectangular matrix (rows != columns)."""
+    torch.manual_seed(3)
+    E = torch.exp(torch.randn(12, 7, dtype=torch.float64) * 0.5).requires_grad_(True)
+    dM = torch.randn(12, 7, dtype=torch.float64)
+    out = oracle.sinkhorn_knopp(E, 9, 1e-6)
+    (out * dM).sum().backward()
+    d = oracle.sinkhorn_backward(dM, E.detach(), 9, 1e-6)
+    assert float((d - E.grad).abs().max() / E.grad.abs().max()) < 1e-10

@@ -86,3 +86,38 @@ def test_abi_rejects_bad_arguments():
     assert b"aligned" in h.mhc_status_string(4)
     with pytest.raises(RuntimeError):
         capi.dynamic_fwd(torch.zeros(2, 4, 64), None, None, None, None, 20, 1e-5)  # CPU tensor
+
+
+@pytest.mark.parametrize("M,N", [(33, 33), (64, 64), (128, 128), (100, 80), (5, 128), (128, 3),
+                                 (1, 7), (7, 1), (48, 96)])
+def test_sinkhorn_single_matrix_up_to_128(M, N):
+    """One [M, N] matrix beyond the batched square kernels: the shape range of the reference's
+    single-matrix op (src/csrc/kernels/sinkhorn_knopp.cuh:423-459), rectangular included, forward
+    and exact backward against the oracle (its backward is checked against autograd on the CPU)."""
+    gen = torch.Generator().manual_seed(1000 * M + N)
+    E = torch.exp(torch.randn(M, N, generator=gen) * 0.5)
+    dM = torch.randn(M, N, generator=gen)
+    out = capi.sinkhorn_fwd(E.cuda(), 20, 1e-6)
+    assert_rel(out, oracle.sinkhorn_knopp(E.double(), 20, 1e-6), 1e-5, "fwd")
+    d = capi.sinkhorn_bwd(dM.cuda(), E.cuda(), 20, 1e-6)
+    assert_rel(d, oracle.sinkhorn_backward(dM.double(), E.double(), 20, 1e-6), 1e-5, "bwd")
+
+
+def test_sinkhorn_single_matrix_through_autograd():
+    """mhc.sinkhorn_knopp on a 64 x 64 and on a 100 x 80 matrix, gradient through the extension."""
+    import mhc
+    for M, N in ((64, 64), (100, 80)):
+        gen = torch.Generator().manual_seed(M)
+        E = torch.exp(torch.randn(M, N, generator=gen) * 0.5)
+        dM = torch.randn(M, N, generator=gen)
+        inp = E.cuda().requires_grad_(True)
+        out = mhc.sinkhorn_knopp(inp, 20, 1e-6)
+        out.backward(dM.cuda())
+        assert_rel(out.detach(), oracle.sinkhorn_knopp(E.double(), 20, 1e-6), 1e-5, "fwd")
+        assert_rel(inp.grad, oracle.sinkhorn_backward(dM.double(), E.double(), 20, 1e-6), 1e-5, "bwd")
+
+
+def test_sinkhorn_single_matrix_rejects_large():
+    big = torch.rand(129, 4, device="cuda")
+    with pytest.raises(Exception):
+        capi.sinkhorn_fwd(big, 5, 1e-6)
