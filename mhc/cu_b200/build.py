@@ -103,10 +103,36 @@ def build_ext(force=False, verbose=False):
     return out
 
 
+ROOT = os.path.dirname(os.path.dirname(HERE))
+ORACLE_C = os.path.join(ROOT, "oracle", "naive_mhc.c")
+ORACLE_LIB = os.path.join(ROOT, "oracle", "_build", "libnaive_mhc.so")
+NATIVE_SRC = os.path.join(ROOT, "tests", "native", "abi_check.cu")
+NATIVE_BIN = os.path.join(ROOT, "tests", "native", "abi_check")
+
+
+def build_checkers(force=False, verbose=False):
+    """Test infrastructure, not part of the product: the C restatement of the naive layer
+    (oracle/naive_mhc.c -> oracle/_build/libnaive_mhc.so, gcc) and the torch-free harness over the
+    C ABI (tests/native/abi_check.cu -> tests/native/abi_check, nvcc, linked against the library
+    and the C oracle)."""
+    if not os.path.exists(ORACLE_C):
+        return
+    hdr = os.path.join(ROOT, "oracle", "naive_mhc.h")
+    if force or not _newer(ORACLE_LIB, [ORACLE_C, hdr]):
+        os.makedirs(os.path.dirname(ORACLE_LIB), exist_ok=True)
+        _run(["gcc", "-O2", "-shared", "-fPIC", "-o", ORACLE_LIB, ORACLE_C, "-lm"], verbose)
+    if os.path.exists(NATIVE_SRC) and (force or not _newer(
+            NATIVE_BIN, [NATIVE_SRC, ORACLE_C, hdr, LIB, os.path.join(INCLUDE, "mhc_b200.h")])):
+        _run([_nvcc(), "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-o",
+              NATIVE_BIN, NATIVE_SRC, ORACLE_C, "-L" + HERE, "-lmhc_b200", "-Xlinker", "-rpath",
+              "-Xlinker", "$ORIGIN/../../mhc/cu_b200"], verbose)
+
+
 def build(force=False, verbose=False, ext=True):
     build_lib(force, verbose)
     if ext:
         build_ext(force, verbose)
+    build_checkers(force, verbose)
 
 
 if __name__ == "__main__":

@@ -262,8 +262,8 @@ coeffs_static_bwd_kernel(float* __restrict__ d_H_pre, float* __restrict__ d_H_po
                          float* __restrict__ d_H_res, const float* __restrict__ dH,
                          const float* __restrict__ H_pre_act, const float* __restrict__ H_post_act,
                          const float* __restrict__ H_res, A* __restrict__ den_ws, int64_t B, int n,
-                         int iters, float eps, int P, int TL) {
-    extern __shared__ float sm[];  // [TL][K] partial sums, then row 0 holds the totals
+                         int iters, float eps, int P, int TL, int den_smem_off) {
+    extern __shared__ __align__(16) float sm[];  // [TL][K] partial sums, then row 0 holds the totals
     const int K = 2 * n + n * n;
     const int e0 = threadIdx.x % P;
     const int tl = threadIdx.x / P;
@@ -298,7 +298,12 @@ coeffs_static_bwd_kernel(float* __restrict__ d_H_pre, float* __restrict__ d_H_po
             }
         }
     }
-    A* den = den_ws + (int64_t)lane_row * 2 * iters;
+    // the step denominators live in shared memory behind the partial sums when they fit (a chain
+    // of 2 * iters dependent round trips to global memory otherwise)
+    A* den = (den_smem_off >= 0)
+                 ? reinterpret_cast<A*>(reinterpret_cast<unsigned char*>(sm) + den_smem_off) +
+                       (int64_t)lane_row * 2 * iters
+                 : den_ws + (int64_t)lane_row * 2 * iters;
     sk_forward<G, A, true>(y, n, row, iters, A(eps), den);
     sk_backward<G, A>(d, y, n, row, iters, den);
     if (act) {
@@ -460,16 +465,20 @@ cudaError_t launch_coeffs_static_bwd(float* d_H_pre, float* d_H_post, float* d_H
     int P = 1;
     while (P < K && P < 1024) P <<= 1;
     const int TL = 1024 / P;
-    const size_t smem = (size_t)TL * K * sizeof(float);
+    const size_t sums = ((size_t)TL * K * sizeof(float) + 15) & ~size_t(15);
     return dispatch_group(d.n, [&]<int G>() -> cudaError_t {
+        const size_t den_bytes = (size_t)G * 2 * iters * (use_double ? sizeof(double) : sizeof(float));
+        const bool den_in_smem = sums + den_bytes <= 40 * 1024;
+        const size_t smem = den_in_smem ? sums + den_bytes : sums;
+        const int den_off = den_in_smem ? (int)sums : -1;
         if (use_double)
             coeffs_static_bwd_kernel<G, double><<<1, 1024, smem, s>>>(
                 d_H_pre, d_H_post, d_H_res, dH, H_pre_act, H_post_act, H_res, (double*)den_ws, d.B,
-                d.n, iters, eps, P, TL);
+                d.n, iters, eps, P, TL, den_off);
         else
             coeffs_static_bwd_kernel<G, float><<<1, 1024, smem, s>>>(
                 d_H_pre, d_H_post, d_H_res, dH, H_pre_act, H_post_act, H_res, (float*)den_ws, d.B,
-                d.n, iters, eps, P, TL);
+                d.n, iters, eps, P, TL, den_off);
         return launched();
     });
 }

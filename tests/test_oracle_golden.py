@@ -79,3 +79,38 @@ def test_oracle_matches_live_reference():
     ref = mod._naive_mhc_dynamic(*args, 20, 1e-5)
     ours = oracle.mhc_dynamic(*args, 20, 1e-5)
     assert_rel(ours, ref, 1e-13, "y live")
+
+
+# ---- the C restatement used by the torch-free native harness ------------------------------------
+def _c_oracle():
+    import ctypes
+
+    from mhc.cu_b200 import build
+    build.build_checkers()
+    lib = ctypes.CDLL(build.ORACLE_LIB)
+    lib.naive_mhc_dynamic_forward.restype = ctypes.c_int
+    return lib
+
+
+@pytest.mark.parametrize("name", golden_names("dyn"))
+def test_c_oracle_forward_matches_golden(name):
+    """oracle/naive_mhc.c (plain C, fp64) against the vectors drawn from the reference's naive layer."""
+    import ctypes
+
+    import numpy as np
+    g = load_golden(name)
+    x = np.ascontiguousarray(g["x"].double().numpy())
+    B, n, C = x.shape
+    phi = np.ascontiguousarray(np.concatenate(
+        [g[k].double().numpy() for k in ("phi_pre", "phi_post", "phi_res")], 0))
+    alpha = np.array([float(g["alpha_pre"]), float(g["alpha_post"]), float(g["alpha_res"])])
+    bias = np.concatenate([g[k].double().numpy().ravel() for k in ("b_pre", "b_post", "b_res")])
+    w = np.ascontiguousarray(g["rmsnorm_weight"].double().numpy())
+    y = np.empty_like(x)
+    ptr = lambda a: a.ctypes.data_as(ctypes.c_void_p)   # noqa: E731
+    rc = _c_oracle().naive_mhc_dynamic_forward(
+        ptr(x), ptr(w), ptr(phi), ptr(alpha), ptr(bias), ctypes.c_long(B), int(n), ctypes.c_long(C),
+        int(g["iters"]), ctypes.c_double(float(g["eps"])), ptr(y))
+    assert rc == 0
+    ref = g["y"].double().numpy()
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-12
