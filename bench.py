@@ -198,6 +198,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the workload's B tokens are split over the ranks")
+    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "p2p"],
+                    help="gradient all-reduce: NCCL, or the library's one-kernel sum over NVLink "
+                         "peer memory (mhc_grad_allreduce_p2p)")
     ap.add_argument("--exposed-allreduce", action="store_true",
                     help="issue the gradient all-reduce on the compute stream after every step "
                          "instead of overlapping it with the next step")
@@ -263,8 +266,21 @@ def main():
     # flat gradient bucket the backward writes into and the ranks all-reduce
     # With more than one rank there are two buckets, used by alternating input sets: while one is
     # being all-reduced on the communication stream the next step writes the other.
-    from mhc.cu_b200.distributed import GradBucket
-    buckets = [GradBucket(n, C, dev) for _ in range(2 if world > 1 else 1)]
+    from mhc.cu_b200.distributed import GradBucket, PeerAllReduce
+    peer = None
+    if world > 1 and args.allreduce == "p2p":
+        # the two buckets live in memory the other ranks have mapped; the sums land in `peer_out`
+        peer = PeerAllReduce(GradBucket.numel(n, C), dev)
+        buckets = [GradBucket(n, C, dev, flat=peer.buckets[k]) for k in range(2)]
+        peer_out = [torch.empty_like(peer.buckets[k]) for k in range(2)]
+    else:
+        buckets = [GradBucket(n, C, dev) for _ in range(2 if world > 1 else 1)]
+
+    def all_reduce_bucket(b, stream):
+        if peer is not None:
+            peer.all_reduce(b, out=peer_out[b], stream=stream.cuda_stream)
+        else:
+            dist.all_reduce(buckets[b].flat)
     ws_f = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag) + 16,
                        dtype=torch.uint8, device=dev)
     ws_b = torch.empty(capi.workspace_bytes(L.OP_DYNAMIC_BWD, B, n, C, iters, tag) + 16,
@@ -298,14 +314,14 @@ def main():
         # the communication stream so that it overlaps the next step (as a data-parallel trainer
         # overlaps it with the backward of the other layers)
         if world > 1 and args.exposed_allreduce:
-            dist.all_reduce(buckets[r % len(buckets)].flat)
+            all_reduce_bucket(r % len(buckets), torch.cuda.current_stream())
         elif world > 1:
             b = r % len(buckets)
             main = torch.cuda.current_stream()
             ready[b].record(main)
             comm.wait_event(ready[b])
             with torch.cuda.stream(comm):
-                dist.all_reduce(buckets[b].flat)
+                all_reduce_bucket(b, comm)
                 reduced[b].record(comm)
             in_flight[b] = True
 
@@ -345,8 +361,9 @@ def main():
                 with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     launch_step(r, torch.cuda.current_stream().cuda_stream)
                 graphs.append(g)
-            graph_note = "cuda graph replay" + ((" + all-reduce after the step" if args.exposed_allreduce
-                                                 else " + all-reduce on a second stream") if world > 1 else "")
+            kind = "peer-memory all-reduce kernel" if peer is not None else "NCCL all-reduce"
+            graph_note = "cuda graph replay" + ((f" + {kind} after the step" if args.exposed_allreduce
+                                                 else f" + {kind} on a second stream") if world > 1 else "")
         except Exception as e:  # capture of the collective can be refused; fall back to eager
             graphs = None
             graph_note = f"python launches (graph capture failed: {type(e).__name__})"
@@ -525,6 +542,9 @@ def main():
                           f"{B}-token batch, fp32, median {med * 1e3:.0f} ms",
                 "host_cpus": os.cpu_count()}
         print(json.dumps(line), flush=True)
+    if peer is not None:
+        peer.check_status()   # a peer wait that ran out would have left its mark here
+        peer.close()
     if world > 1:
         dist.destroy_process_group()
     return 0

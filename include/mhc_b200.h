@@ -171,6 +171,33 @@ int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp,
                           int iters, float eps, void* workspace, size_t workspace_bytes,
                           mhc_stream_t stream);
 
+/* ---- data-parallel gradient all-reduce over NVLink peer memory (no counterpart in the single-GPU
+ * AndreSlavescu/mHC.cu; replaces the NCCL all-reduce a trainer issues after the layer's backward) ----
+ *
+ * mhc_p2p_alloc: cudaMalloc of `bytes` (zero-filled) on the current device plus the 64-byte CUDA
+ * IPC handle under which the other ranks of the node map it.  mhc_p2p_open maps a peer's handle
+ * into this process (peer access enabled lazily) and returns the local address; mhc_p2p_close
+ * undoes it; mhc_p2p_free releases an allocation of mhc_p2p_alloc.  Host-synchronous set-up
+ * calls, not for the hot path. */
+int mhc_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[64]);
+int mhc_p2p_open(void** ptr, const unsigned char handle[64]);
+int mhc_p2p_close(void* ptr);
+int mhc_p2p_free(void* ptr);
+
+/* out[i] = sum over ranks r = 0 .. world-1 (in that order on every rank, so all ranks get the same
+ * bits) of bucket_r[i], i < count, fp32.  bufs[r] / flags[r] (HOST arrays of `world` pointers): the
+ * addresses, valid on THIS GPU, of rank r's bucket and of rank r's row of `world` 32-bit flags
+ * (own allocation for r == rank, mhc_p2p_open for the others; flags start at zero).  `seq` is the
+ * step number: it has to grow by one with every call, identically on all ranks, starting at 1.
+ * The caller alternates between two buckets (out may be any local buffer).  The kernel publishes
+ * "bucket seq complete" to every peer, waits — at most about a second, then it ORs 2 into
+ * *status (device memory, may be NULL) and leaves `out` untouched — for every peer's flag, and
+ * adds.  world <= 16; one rank per GPU: ranks that share a GPU would wait on one another inside
+ * one device and must not use this call. */
+int mhc_grad_allreduce_p2p(float* out, const void* const* bufs, void* const* flags, int rank,
+                           int world, int64_t count, unsigned seq, int* status,
+                           mhc_stream_t stream);
+
 /* Same result as mhc_sinkhorn_bwd, for callers that cannot supply a workspace at all: a plug-in
  * inside a host that owns every byte of device memory and exposes no allocator, or a caller that
  * may not use cudaMalloc where it runs.  (No counterpart in AndreSlavescu/mHC.cu, whose bindings

@@ -33,6 +33,11 @@ SIGNATURES = {
     "mhc_sinkhorn_bwd": (_i, [_p, _p, _p, _l, _i, _i, _f, _p, _z, _p]),
     "mhc_sinkhorn_rect_fwd": (_i, [_p, _p, _i, _i, _i, _f, _p]),
     "mhc_sinkhorn_rect_bwd": (_i, [_p, _p, _p, _i, _i, _i, _f, _p, _z, _p]),
+    "mhc_p2p_alloc": (_i, [_p, _z, _p]),
+    "mhc_p2p_open": (_i, [_p, _p]),
+    "mhc_p2p_close": (_i, [_p]),
+    "mhc_p2p_free": (_i, [_p]),
+    "mhc_grad_allreduce_p2p": (_i, [_p, _p, _p, _i, _i, _l, C.c_uint, _p, _p]),
     "mhc_sinkhorn_bwd_noalloc": (_i, [_p, _p, _p, _l, _i, _i, _f, _p]),
     "mhc_sinkhorn_bwd_noalloc_capacity": (_z, []),
     "mhc_rmsnorm_fwd": (_i, [_p, _p, _p, _p, _l, _l, _f, _p]),

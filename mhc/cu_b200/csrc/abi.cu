@@ -512,6 +512,59 @@ int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp,
     return MHC_OK;
 }
 
+int mhc_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[64]) {
+    if (!ptr || !handle || bytes == 0) return MHC_ERR_NULL_POINTER;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    MHC_TRY(cudaMalloc(&p, bytes));
+    cudaError_t e = cudaMemset(p, 0, bytes);
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        (void)cudaFree(p);
+        return cuda_fail(e);
+    }
+    std::memcpy(handle, &h, 64);
+    *ptr = p;
+    return MHC_OK;
+}
+
+int mhc_p2p_open(void** ptr, const unsigned char handle[64]) {
+    if (!ptr || !handle) return MHC_ERR_NULL_POINTER;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, 64);
+    MHC_TRY(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return MHC_OK;
+}
+
+int mhc_p2p_close(void* ptr) {
+    if (!ptr) return MHC_ERR_NULL_POINTER;
+    MHC_TRY(cudaIpcCloseMemHandle(ptr));
+    return MHC_OK;
+}
+
+int mhc_p2p_free(void* ptr) {
+    if (!ptr) return MHC_ERR_NULL_POINTER;
+    MHC_TRY(cudaFree(ptr));
+    return MHC_OK;
+}
+
+int mhc_grad_allreduce_p2p(float* out, const void* const* bufs, void* const* flags, int rank,
+                           int world, int64_t count, unsigned seq, int* status,
+                           mhc_stream_t stream) {
+    if (world < 1 || world > 16 || rank < 0 || rank >= world || count < 0) return MHC_ERR_BAD_SHAPE;
+    if (!out || !bufs || !flags) return MHC_ERR_NULL_POINTER;
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r] || !flags[r]) return MHC_ERR_NULL_POINTER;
+        if (!aligned16(bufs[r])) return MHC_ERR_MISALIGNED;
+    }
+    if (!aligned16(out)) return MHC_ERR_MISALIGNED;
+    if (count == 0) return MHC_OK;
+    MHC_TRY(launch_p2p_allreduce(out, bufs, flags, rank, world, count, seq, status,
+                                 reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
 int mhc_rmsnorm_fwd(void* out, float* rms, const void* inp, const void* weight, int64_t B,
                     int64_t C, float eps, mhc_stream_t stream) {
     if (B < 0 || B > 0x7fffffffLL || C < 1) return MHC_ERR_BAD_SHAPE;

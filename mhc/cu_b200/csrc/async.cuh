@@ -11,6 +11,7 @@ namespace mhc {
 
 // error codes a kernel may OR into its device status word
 constexpr int kDevErrBulkWait = 1;   // a bulk-copy wait ran out
+constexpr int kDevErrPeerWait = 2;   // a peer's "bucket ready" flag did not arrive in time
 
 constexpr long long kWaitCycles = 2000000000LL;   // about one second of SM clocks
 

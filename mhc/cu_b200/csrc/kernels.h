@@ -162,6 +162,11 @@ cudaError_t launch_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N,
 cudaError_t launch_sinkhorn_rect_bwd(float* d_inp, const float* grad, const float* inp, void* ws,
                                      int M, int N, int iters, float eps, cudaStream_t s);
 
+// ---- p2p_allreduce.cu: sum of the ranks' gradient buckets over NVLink peer memory ------------
+cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* const* flags, int rank,
+                                 int world, int64_t count, unsigned seq, int* status,
+                                 cudaStream_t s);
+
 // ---- bwd_gram.cu: backward pass A from tensor-core Gram matrices (bf16, n = 4) --------------
 bool bwd_gram_supported(Dims d);
 int bwd_gram_blocks(Dims d);   // rows of `partials` the fused variant writes

@@ -1,0 +1,129 @@
+// All-reduce (sum) of the flat fp32 parameter-gradient bucket over NVLink peer memory, one kernel
+// per rank, for the ~1 MB buckets of this layer where a library all-reduce is all latency.
+//
+// Every rank owns a bucket and a row of `world` flags, both in memory its peers have mapped
+// (CUDA IPC).  One-shot protocol, step number `seq` (increasing by one per call on every rank):
+//   1. the rank publishes "my bucket of step seq is complete" by storing seq into slot [rank] of
+//      every peer's flag row (release, system scope; the kernels that filled the bucket precede
+//      this one in the stream);
+//   2. every block waits until all slots of its own row hold a value >= seq (acquire, system
+//      scope).  The wait is BOUNDED: after kP2PWaitCycles the block ORs an error code into the
+//      status word and the kernel leaves `out` untouched;
+//   3. out[i] = sum over ranks r = 0 .. world-1, in that order on every rank (bitwise identical
+//      results everywhere), of bucket_r[i], read with plain (volatile) 16-byte peer loads.
+// Nothing waits at the end.  The caller alternates between TWO buckets: a rank can only overwrite
+// the bucket of step seq (in step seq + 2) after it has passed the wait of step seq + 1, which
+// needs every peer's signal seq + 1, which a peer sends only after it has finished reading step
+// seq.  Peers are separate GPUs; nothing here may be used between kernels sharing one GPU.
+//
+// No counterpart in AndreSlavescu/mHC.cu (single GPU).  Replaces the NCCL all-reduce a
+// data-parallel trainer issues after the layer's backward.
+#include "async.cuh"
+#include "kernels.h"
+
+namespace mhc {
+
+namespace {
+
+constexpr long long kP2PWaitCycles = 2000000000LL;   // about one second of SM clocks
+constexpr int kP2PThreads = 512;
+constexpr int kP2PMaxWorld = 16;
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.global.release.sys.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.global.acquire.sys.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// 16-byte load that is never served from a stale cached copy of a peer's memory
+__device__ __forceinline__ float4 ld_peer4(const float4* p) {
+    float4 v;
+    asm volatile("ld.volatile.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+
+struct P2PTable {
+    const float* buf[kP2PMaxWorld];
+    unsigned* flags[kP2PMaxWorld];
+};
+
+__global__ void __launch_bounds__(kP2PThreads)
+p2p_allreduce_kernel(float* __restrict__ out, const P2PTable tab, int rank, int world, int64_t count,
+                     unsigned seq, int* __restrict__ status) {
+    __shared__ int ok_s;
+    const int tid = threadIdx.x;
+    if (blockIdx.x == 0 && tid < world) {
+        __threadfence_system();
+        st_release_sys(tab.flags[tid] + rank, seq);
+    }
+    if (tid == 0) {
+        int ok = 1;
+        const long long t0 = clock64();
+        for (int r = 0; r < world && ok; ++r) {
+            // values only grow; the unsigned difference handles the wrap of the counter
+            while ((int)(ld_acquire_sys(tab.flags[rank] + r) - seq) < 0) {
+                if (clock64() - t0 > kP2PWaitCycles) {
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+        ok_s = ok;
+        if (!ok && status != nullptr) atomicOr(status, kDevErrPeerWait);
+    }
+    __syncthreads();
+    if (!ok_s) return;
+
+    const int64_t n4 = count / 4;
+    const int64_t stride = (int64_t)gridDim.x * kP2PThreads;
+    for (int64_t i = (int64_t)blockIdx.x * kP2PThreads + tid; i < n4; i += stride) {
+        // all peers' loads of this element are in flight together (one NVLink round trip), the
+        // additions then run in rank order
+        float4 v[kP2PMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kP2PMaxWorld; ++r)
+            if (r < world) v[r] = ld_peer4(reinterpret_cast<const float4*>(tab.buf[r]) + i);
+        float4 acc = v[0];
+#pragma unroll
+        for (int r = 1; r < kP2PMaxWorld; ++r) {
+            if (r < world) {
+                acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
+            }
+        }
+        reinterpret_cast<float4*>(out)[i] = acc;
+    }
+    if (blockIdx.x == 0) {   // tail of a count that is not a multiple of four
+        for (int64_t i = n4 * 4 + tid; i < count; i += kP2PThreads) {
+            float acc = *reinterpret_cast<const volatile float*>(tab.buf[0] + i);
+            for (int r = 1; r < world; ++r) acc += *reinterpret_cast<const volatile float*>(tab.buf[r] + i);
+            out[i] = acc;
+        }
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* const* flags, int rank,
+                                 int world, int64_t count, unsigned seq, int* status,
+                                 cudaStream_t s) {
+    if (world < 1 || world > kP2PMaxWorld || rank < 0 || rank >= world) return cudaErrorInvalidValue;
+    P2PTable tab{};
+    for (int r = 0; r < world; ++r) {
+        tab.buf[r] = static_cast<const float*>(bufs[r]);
+        tab.flags[r] = static_cast<unsigned*>(flags[r]);
+    }
+    int64_t blocks = (count / 4 + kP2PThreads - 1) / kP2PThreads;
+    if (blocks > 64) blocks = 64;   // a few blocks per rank: the bucket is small, the SMs are busy
+    if (blocks < 1) blocks = 1;
+    p2p_allreduce_kernel<<<(unsigned)blocks, kP2PThreads, 0, s>>>(out, tab, rank, world, count, seq,
+                                                                status);
+    return launched();
+}
+
+}  // namespace mhc

@@ -23,12 +23,22 @@ def shard_bounds(total: int, rank: int, world: int):
 class GradBucket:
     """Flat fp32 gradient buffer of one dynamic-H layer with typed views into it."""
 
-    def __init__(self, n: int, C: int, device):
+    @staticmethod
+    def numel(n: int, C: int) -> int:
+        K = 2 * n + n * n
+        return K * n * C + K + 4 + C
+
+    def __init__(self, n: int, C: int, device, flat=None):
+        """``flat``: an existing fp32 tensor of ``GradBucket.numel(n, C)`` elements to lay the views
+        over (for instance a bucket of :class:`PeerAllReduce`); allocated here when omitted."""
         self.n, self.C = n, C
         K, nC = 2 * n + n * n, n * C
         self.K, self.nC = K, nC
         sizes = [K * nC, K, 4, C]                 # alpha padded to 4 so every slice is 16-byte aligned
-        self.flat = torch.zeros(sum(sizes), dtype=torch.float32, device=device)
+        if flat is None:
+            flat = torch.zeros(sum(sizes), dtype=torch.float32, device=device)
+        assert flat.dtype == torch.float32 and flat.numel() == sum(sizes) and flat.is_contiguous()
+        self.flat = flat
         o = 0
         self.d_phi = self.flat[o:o + K * nC].view(K, nC); o += K * nC
         self.d_bias = self.flat[o:o + K]; o += K
@@ -56,3 +66,87 @@ class GradBucket:
             "b_pre": self.d_bias[:n], "b_post": self.d_bias[n:2 * n],
             "b_res": self.d_bias[2 * n:].view(n, n),
         }
+
+
+class _RawCuda:
+    """A device address as an object torch can wrap (CUDA array interface, fp32 vector)."""
+
+    def __init__(self, ptr: int, numel: int):
+        self.__cuda_array_interface__ = {"shape": (numel,), "typestr": "<f4", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+class PeerAllReduce:
+    """Gradient buckets in memory the other ranks of the node have mapped (CUDA IPC through the C
+    ABI's ``mhc_p2p_*`` calls) and the one-kernel all-reduce over them (``mhc_grad_allreduce_p2p``:
+    every rank signals its peers, waits — bounded — for their signals and sums all buckets over
+    NVLink in rank order).
+
+    ``buckets[k]`` (k = 0, 1) are flat fp32 tensors of ``numel`` elements to write gradients into;
+    consecutive steps must alternate between them.  ``all_reduce(k, out)`` leaves the sum over all
+    ranks in ``out`` (a local tensor, default: an internal one returned by the call).  One rank per
+    GPU; the process group is only used to exchange the 64-byte handles at construction."""
+
+    def __init__(self, numel: int, device, group=None):
+        import ctypes as C
+
+        from . import _lib as L
+        self._L, self._C = L, C
+        lib = L.lib()
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.numel, self.device = int(numel), torch.device(device)
+        bucket_bytes = (self.numel * 4 + 255) // 256 * 256
+        total = 2 * bucket_bytes + 256                     # two buckets, then the row of flags
+        with torch.cuda.device(self.device):
+            base, handle = C.c_void_p(), (C.c_ubyte * 64)()
+            L.check(lib.mhc_p2p_alloc(C.byref(base), total, handle), "mhc_p2p_alloc")
+            self._base = base.value
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            self._peer_base = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    self._peer_base.append(self._base)
+                else:
+                    p = C.c_void_p()
+                    hb = (C.c_ubyte * 64).from_buffer_copy(h)
+                    L.check(lib.mhc_p2p_open(C.byref(p), hb), "mhc_p2p_open")
+                    self._peer_base.append(p.value)
+        arr = C.c_void_p * self.world
+        self._bufs = [arr(*[b + k * bucket_bytes for b in self._peer_base]) for k in range(2)]
+        self._flags = arr(*[b + 2 * bucket_bytes for b in self._peer_base])
+        self.buckets = [torch.as_tensor(_RawCuda(self._base + k * bucket_bytes, self.numel),
+                                        device=self.device) for k in range(2)]
+        self._out = torch.empty(self.numel, dtype=torch.float32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.seq = 0
+        dist.barrier(group=group)   # every rank has mapped every bucket before the first use
+
+    def all_reduce(self, k: int, out=None, stream=None):
+        out = self._out if out is None else out
+        assert out.dtype == torch.float32 and out.numel() >= self.numel and out.is_contiguous()
+        self.seq += 1
+        s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
+        C = self._C
+        st = self._L.lib().mhc_grad_allreduce_p2p(
+            C.c_void_p(out.data_ptr()), self._bufs[k], self._flags, self.rank, self.world,
+            self.numel, C.c_uint(self.seq & 0xFFFFFFFF), C.c_void_p(self.status.data_ptr()),
+            C.c_void_p(s))
+        self._L.check(st, "mhc_grad_allreduce_p2p")
+        return out
+
+    def check_status(self):
+        """Host read of the device status word (synchronises): raises if a peer wait ran out."""
+        v = int(self.status.item())
+        if v != 0:
+            raise RuntimeError(f"peer all-reduce reported device status {v} (2 = a peer's flag did "
+                               "not arrive within the wait limit)")
+
+    def close(self):
+        lib = self._L.lib()
+        torch.cuda.synchronize(self.device)
+        for r, b in enumerate(self._peer_base):
+            if r != self.rank:
+                lib.mhc_p2p_close(self._C.c_void_p(b))
+        lib.mhc_p2p_free(self._C.c_void_p(self._base))
+        self._peer_base = []

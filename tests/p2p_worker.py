@@ -1,0 +1,75 @@
+"""Worker of tests/test_gpu_p2p.py (one process per GPU, launched with torch.distributed.run):
+the peer-memory all-reduce of the gradient bucket against NCCL's, over several alternating steps."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from mhc.cu_b200.distributed import GradBucket, PeerAllReduce  # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank)))
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    n, C = 4, 2560
+    numel = GradBucket.numel(n, C)
+    par = PeerAllReduce(numel, dev)
+    views = [GradBucket(n, C, dev, flat=par.buckets[k]) for k in range(2)]
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    ok = True
+    outs = []
+    for step in range(7):
+        k = step % 2
+        data = torch.randn(numel, device=dev, generator=gen)
+        par.buckets[k].copy_(data)
+        assert views[k].d_rmsnorm_weight.data_ptr() == par.buckets[k].data_ptr() + 4 * (numel - C)
+        out = par.all_reduce(k).clone()
+        ref = data.clone()
+        dist.all_reduce(ref)
+        err = float((out - ref).abs().max() / ref.abs().max())
+        ok = ok and err < 1e-6
+        outs.append(out)
+    par.check_status()
+    # every rank holds the same bits
+    mine = torch.stack(outs)
+    gathered = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(gathered, mine)
+    same = all(torch.equal(g, gathered[0]) for g in gathered)
+    # timing: 200 all-reduces back to back (alternating buckets), device time
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(200):
+        par.all_reduce(i % 2)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / 200
+    par.check_status()
+    t = torch.tensor([us], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ref = torch.zeros(numel, device=dev)
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for i in range(200):
+        dist.all_reduce(ref)
+    e1.record()
+    torch.cuda.synchronize()
+    t2 = torch.tensor([e0.elapsed_time(e1) * 1e3 / 200], device=dev)
+    dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        print(f"p2p all-reduce of {numel * 4 / 1e6:.2f} MB over {world} GPUs: parity {'ok' if ok else 'BAD'}, "
+              f"identical bits on all ranks: {same}, {float(t):.1f} us per call "
+              f"(NCCL all_reduce: {float(t2):.1f} us)", flush=True)
+    par.close()
+    dist.destroy_process_group()
+    return 0 if (ok and same) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
