@@ -86,6 +86,14 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def begin(self):
+        """Called right before the timed region: earlier samples (set-up, idle) are not used."""
+        self.first = 0
+        try:
+            self.first = sum(1 for _ in open(self.path))
+        except Exception:
+            pass
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
@@ -104,6 +112,9 @@ class ClockSampler:
             os.unlink(self.path)
         except Exception:
             pass
+        first = getattr(self, "first", 0)
+        if len(rows) - first >= 2:
+            rows = rows[first:]
         if rows:
             clocks = sorted(int(r[0]) for r in rows)
             # the busy half of the samples: the sampler also sees idle time around the region
@@ -245,6 +256,9 @@ def main():
         B = hi - lo   # ranks may differ by one token; the slowest rank sets the time
     K = 2 * n + n * n
     iters, eps = cfg["iters"], cfg["eps"]
+    # nvidia-smi needs a second or two to enumerate a full node before its first sample: start it
+    # now, so that it is looping by the time the timed region begins
+    sampler = ClockSampler(local_rank) if not args.profile else None
     tag = L.BF16 if dtype == torch.bfloat16 else L.F32
     io_bytes = 2 if dtype == torch.bfloat16 else 4
     params, (w, phi, alpha, bias) = make_problem(cfg, dev, 0)
@@ -390,10 +404,11 @@ def main():
     drain()
     barrier()
     mark("warm-up done")
-    sampler = ClockSampler(local_rank) if not args.profile else None
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     barrier()
+    if sampler is not None:
+        sampler.begin()
     e0.record()
     for i in range(args.steps):
         step(i)
@@ -415,7 +430,7 @@ def main():
         return 0
     # Untimed extra load so the 50 ms clock sampler surely sees the GPU busy.  The step count is
     # derived from the rank-agreed time, so every rank issues the same number of all-reduces.
-    extra = max(1, min(20000, int(400.0 / max(ms / args.steps, 1e-3))))
+    extra = max(1, min(40000, int((400.0 if world < 4 else 1500.0) / max(ms / args.steps, 1e-3))))
     for i in range(extra):
         step(i)
     torch.cuda.synchronize()
