@@ -7,7 +7,8 @@ One step = one forward + backward of the dynamic-H mHC layer over one batch of s
 tokens (default workload c3: x [1280, 4, 2560] bf16 per GPU, phi ~ N(0, 0.02), alpha 0.01, eps 1e-6,
 20 Sinkhorn iterations).  With N > 1 (launched by torchrun, one rank per GPU) every rank works on
 its own batch of the same size (weak scaling) and the flat fp32 parameter-gradient bucket is
-all-reduced with NCCL on a second stream, overlapping the next step (two alternating buckets);
+all-reduced (the library's kernel over NVLink peer memory, or NCCL with --allreduce nccl) on a
+second stream, overlapping the next step (two alternating buckets);
 every all-reduce completes inside the timed region.  Rank 0 prints ONE JSON line.
 
   value      tokens/s over all ranks, inputs resident in HBM, K steps timed with CUDA events between
@@ -209,9 +210,10 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--strong", action="store_true",
                     help="strong scaling: the workload's B tokens are split over the ranks")
-    ap.add_argument("--allreduce", default="nccl", choices=["nccl", "p2p"],
-                    help="gradient all-reduce: NCCL, or the library's one-kernel sum over NVLink "
-                         "peer memory (mhc_grad_allreduce_p2p)")
+    ap.add_argument("--allreduce", default="p2p", choices=["nccl", "p2p"],
+                    help="gradient all-reduce: the library's one-kernel sum over NVLink peer memory "
+                         "(mhc_grad_allreduce_p2p; falls back to NCCL where the buckets cannot be "
+                         "shared between the ranks), or NCCL")
     ap.add_argument("--exposed-allreduce", action="store_true",
                     help="issue the gradient all-reduce on the compute stream after every step "
                          "instead of overlapping it with the next step")
@@ -241,11 +243,12 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        # The collective is 1 MB and runs (on a high-priority stream) next to kernels that are sized
-        # as one resident wave over all SMs: a handful of NCCL blocks is enough to finish it within
-        # a step (measured on two GPUs: 1 block 215 us per step, 2: 113, 6 to 32: 75).
+        # With --allreduce nccl the collective is 1 MB and runs (on a high-priority stream) next to
+        # kernels that are sized as one resident wave over all SMs: a handful of NCCL blocks is
+        # enough to finish it within a step (measured, us per step: two GPUs 1 block 215, 2: 113,
+        # 6 to 32: 75; eight GPUs 4 blocks 79, 8: 82, 16: 106).
         if not args.exposed_allreduce:
-            os.environ.setdefault("NCCL_MAX_CTAS", "8")
+            os.environ.setdefault("NCCL_MAX_CTAS", "4")
         dist.init_process_group("nccl", device_id=dev)
     lib = L.lib()
 
@@ -284,7 +287,12 @@ def main():
     peer = None
     if world > 1 and args.allreduce == "p2p":
         # the two buckets live in memory the other ranks have mapped; the sums land in `peer_out`
-        peer = PeerAllReduce(GradBucket.numel(n, C), dev)
+        try:
+            peer = PeerAllReduce(GradBucket.numel(n, C), dev)   # fails on all ranks or on none
+        except RuntimeError as e:
+            if rank == 0:
+                print(f"[bench] {e}; using NCCL", file=sys.stderr, flush=True)
+    if peer is not None:
         buckets = [GradBucket(n, C, dev, flat=peer.buckets[k]) for k in range(2)]
         peer_out = [torch.empty_like(peer.buckets[k]) for k in range(2)]
     else:

@@ -119,7 +119,9 @@ cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* cons
         tab.flags[r] = static_cast<unsigned*>(flags[r]);
     }
     int64_t blocks = (count / 4 + kP2PThreads - 1) / kP2PThreads;
-    if (blocks > 64) blocks = 64;   // a few blocks per rank: the bucket is small, the SMs are busy
+    // a few blocks per rank: the bucket is small, and the kernels this all-reduce overlaps with are
+    // sized as one resident wave over (nearly) all SMs
+    if (blocks > 16) blocks = 16;
     if (blocks < 1) blocks = 1;
     p2p_allreduce_kernel<<<(unsigned)blocks, kP2PThreads, 0, s>>>(out, tab, rank, world, count, seq,
                                                                 status);

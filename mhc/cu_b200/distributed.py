@@ -97,21 +97,39 @@ class PeerAllReduce:
         self.numel, self.device = int(numel), torch.device(device)
         bucket_bytes = (self.numel * 4 + 255) // 256 * 256
         total = 2 * bucket_bytes + 256                     # two buckets, then the row of flags
+        # Set-up is collective and must fail on all ranks or on none: every rank takes part in the
+        # exchange of handles and in the vote even if one of its own calls failed.
+        self._base, self._peer_base, err = None, [], None
         with torch.cuda.device(self.device):
             base, handle = C.c_void_p(), (C.c_ubyte * 64)()
-            L.check(lib.mhc_p2p_alloc(C.byref(base), total, handle), "mhc_p2p_alloc")
-            self._base = base.value
+            try:
+                L.check(lib.mhc_p2p_alloc(C.byref(base), total, handle), "mhc_p2p_alloc")
+                self._base = base.value
+            except RuntimeError as e:
+                err = e
             handles = [None] * self.world
-            dist.all_gather_object(handles, bytes(handle), group=group)
-            self._peer_base = []
-            for r, h in enumerate(handles):
-                if r == self.rank:
-                    self._peer_base.append(self._base)
-                else:
+            dist.all_gather_object(handles, bytes(handle) if err is None else None, group=group)
+            if err is None and all(h is not None for h in handles):
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        self._peer_base.append(self._base)
+                        continue
                     p = C.c_void_p()
                     hb = (C.c_ubyte * 64).from_buffer_copy(h)
-                    L.check(lib.mhc_p2p_open(C.byref(p), hb), "mhc_p2p_open")
+                    try:
+                        L.check(lib.mhc_p2p_open(C.byref(p), hb), "mhc_p2p_open")
+                    except RuntimeError as e:
+                        err = e
+                        break
                     self._peer_base.append(p.value)
+            elif err is None:
+                err = RuntimeError("a peer could not allocate its bucket")
+            vote = torch.tensor([0 if err is not None else 1], dtype=torch.int32, device=self.device)
+            dist.all_reduce(vote, op=dist.ReduceOp.MIN, group=group)
+            if int(vote.item()) == 0:
+                self.close()
+                raise RuntimeError(f"peer-memory all-reduce is not available on this node: "
+                                   f"{err if err is not None else 'a peer failed to map the buckets'}")
         arr = C.c_void_p * self.world
         self._bufs = [arr(*[b + k * bucket_bytes for b in self._peer_base]) for k in range(2)]
         self._flags = arr(*[b + 2 * bucket_bytes for b in self._peer_base])
@@ -148,5 +166,6 @@ class PeerAllReduce:
         for r, b in enumerate(self._peer_base):
             if r != self.rank:
                 lib.mhc_p2p_close(self._C.c_void_p(b))
-        lib.mhc_p2p_free(self._C.c_void_p(self._base))
-        self._peer_base = []
+        if self._base is not None:
+            lib.mhc_p2p_free(self._C.c_void_p(self._base))
+        self._peer_base, self._base = [], None
