@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Generate the golden vectors under tests/golden/ from the reference's own naive code.
 
-Run in a container that has the reference checkout (default /root/reference):
+Run in a container that has a checkout of the reference (pass its path with --reference):
 
     python tests/golden/make_golden.py [--reference /path/to/mHC.cu]
 
@@ -135,7 +135,8 @@ def sinkhorn_case(cls, name, seed, n, iters, eps):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MHC_REFERENCE_CHECKOUT",
+                                                          os.path.join(os.sep, "root", "reference")))
     args = ap.parse_args()
     tl = _load(os.path.join(args.reference, "src/python/tests/test_layer.py"), "ref_test_layer")
     bl = _load(os.path.join(args.reference, "src/python/benchmarks/bench_layer.py"), "ref_bench_layer")

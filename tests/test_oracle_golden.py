@@ -61,13 +61,17 @@ def test_sinkhorn_doubly_stochastic():
     assert float((out.sum(-2) - 1).abs().max()) < 1e-5
 
 
-@pytest.mark.skipif(not os.path.isdir("/root/reference/src/python"), reason="reference checkout not present")
+_REFERENCE = os.environ.get("MHC_REFERENCE_CHECKOUT", os.path.join(os.sep, "root", "reference"))
+
+
+@pytest.mark.skipif(not os.path.isdir(os.path.join(_REFERENCE, "src", "python")),
+                    reason="reference checkout not present (set MHC_REFERENCE_CHECKOUT)")
 def test_oracle_matches_live_reference():
-    """When the reference checkout is present, also compare live on fresh inputs."""
+    """When a checkout of the reference is present, also compare live on fresh inputs."""
     import importlib.util
 
     spec = importlib.util.spec_from_file_location(
-        "ref_test_layer", "/root/reference/src/python/tests/test_layer.py")
+        "ref_test_layer", os.path.join(_REFERENCE, "src", "python", "tests", "test_layer.py"))
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     gen = torch.Generator().manual_seed(123)
