@@ -52,7 +52,8 @@ enum mhc_op {
     MHC_OP_SINKHORN_BWD = 5,
     MHC_OP_RMSNORM_FWD = 6,
     MHC_OP_RMSNORM_BWD = 7,
-    MHC_OP_SINKHORN_RECT_BWD = 8   /* B = rows M, n = columns N of the single matrix */
+    MHC_OP_SINKHORN_RECT_BWD = 8,  /* B = rows M, n = columns N of the single matrix */
+    MHC_OP_DYNAMIC_PRE_BWD = 9     /* mhc_dynamic_pre_bwd (mhc_dynamic_pre_fwd: MHC_OP_DYNAMIC_FWD) */
 };
 
 /* Human-readable text for an mhc_status.  Never NULL.
@@ -170,6 +171,45 @@ int mhc_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N, int iters,
 int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp, int M, int N,
                           int iters, float eps, void* workspace, size_t workspace_bytes,
                           mhc_stream_t stream);
+
+/* ---- the dynamic-H layer in two halves, for a caller's own sub-layer F between them ----------------
+ * (a transformer block: y_hat -> attention / MLP -> f).  The reference layer is monolithic
+ * (src/python/mhc/layer.py:61-101, mhc_layer_fwd_dynamic src/python/bindings.cu:403-481: aggregate,
+ * RMSNorm, distribute + mix in one call with nothing in between); these four calls cut it between
+ * RMSNorm and distribute + mix.  n <= 8, C a multiple of the 16-byte vector, else
+ * MHC_ERR_UNSUPPORTED.  With f = y_hat, pre + post equal mhc_dynamic_fwd / _bwd.
+ *
+ * pre, forward: coefficients as in mhc_dynamic_fwd, and y_hat [B, C] (stream dtype) =
+ * (sum_i H_pre[i] x[i,:]) / rho * rmsnorm_weight.  Saved: rms [B] (= rho), rms_h [B], H_pre [B,n],
+ * H_post [B,n], M [B,n,n], proj [B,K].  Workspace: MHC_OP_DYNAMIC_FWD. */
+int mhc_dynamic_pre_fwd(void* y_hat, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+                        float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                        const float* alpha, const float* bias, int64_t B, int n, int64_t C,
+                        int iters, float eps, int dtype, void* workspace, size_t workspace_bytes,
+                        mhc_stream_t stream);
+
+/* post, forward: y[b,i,:] = sum_j M[b,i,j] x[b,j,:] + H_post[b,i] f[b,:],  f [B, C] = F(y_hat). */
+int mhc_post_fwd(void* y, const void* x, const void* f, const float* H_post, const float* M,
+                 int64_t B, int n, int64_t C, int dtype, mhc_stream_t stream);
+
+/* post, backward: from dy [B,n,C]:  d_f [B,C] = sum_i H_post[i] dy[i,:];  dx_part [B,n,C] =
+ * M^T dy (the part of dx that flows through the mixing);  dH_post [B,n] = <dy_i, f>;
+ * dM [B,n,n] = <dy_i, x_j>. */
+int mhc_post_bwd(void* dx_part, void* d_f, float* dH_post, float* dM, const void* dy, const void* x,
+                 const void* f, const float* H_post, const float* M, int64_t B, int n, int64_t C,
+                 int dtype, mhc_stream_t stream);
+
+/* pre, backward: from d_y_hat [B,C] (what F's backward returns) and the coefficient gradients
+ * dH_post, dM of mhc_post_bwd: dx [B,n,C] (everything but dx_part) and the parameter gradients
+ * d_rmsnorm_weight [C], d_phi [K,nC], d_alpha [3], d_bias [K] (fp32, written).  Workspace:
+ * MHC_OP_DYNAMIC_PRE_BWD. */
+int mhc_dynamic_pre_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha,
+                        float* d_bias, const void* d_y_hat, const float* dH_post, const float* dM,
+                        const void* x, const void* rmsnorm_weight, const void* phi,
+                        const float* alpha, const float* bias, const float* rms,
+                        const float* rms_h, const float* H_pre, const float* H_post,
+                        const float* proj, int64_t B, int n, int64_t C, int iters, float eps,
+                        int dtype, void* workspace, size_t workspace_bytes, mhc_stream_t stream);
 
 /* ---- data-parallel gradient all-reduce over NVLink peer memory (no counterpart in the single-GPU
  * AndreSlavescu/mHC.cu; replaces the NCCL all-reduce a trainer issues after the layer's backward) ----

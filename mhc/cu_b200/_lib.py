@@ -15,6 +15,7 @@ F32, BF16 = 0, 1
 OP_DYNAMIC_FWD, OP_DYNAMIC_BWD, OP_STATIC_FWD, OP_STATIC_BWD = 0, 1, 2, 3
 OP_SINKHORN_FWD, OP_SINKHORN_BWD, OP_RMSNORM_FWD, OP_RMSNORM_BWD = 4, 5, 6, 7
 OP_SINKHORN_RECT_BWD = 8
+OP_DYNAMIC_PRE_BWD = 9
 
 _p, _i, _l, _f, _z = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
 
@@ -33,6 +34,10 @@ SIGNATURES = {
     "mhc_sinkhorn_bwd": (_i, [_p, _p, _p, _l, _i, _i, _f, _p, _z, _p]),
     "mhc_sinkhorn_rect_fwd": (_i, [_p, _p, _i, _i, _i, _f, _p]),
     "mhc_sinkhorn_rect_bwd": (_i, [_p, _p, _p, _i, _i, _i, _f, _p, _z, _p]),
+    "mhc_dynamic_pre_fwd": (_i, [_p] * 12 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
+    "mhc_post_fwd": (_i, [_p] * 5 + [_l, _i, _l, _i, _p]),
+    "mhc_post_bwd": (_i, [_p] * 9 + [_l, _i, _l, _i, _p]),
+    "mhc_dynamic_pre_bwd": (_i, [_p] * 18 + [_l, _i, _l, _i, _f, _i, _p, _z, _p]),
     "mhc_p2p_alloc": (_i, [_p, _z, _p]),
     "mhc_p2p_open": (_i, [_p, _p]),
     "mhc_p2p_close": (_i, [_p]),

@@ -194,6 +194,74 @@ def static_bwd(dy, x, rmsnorm_weight, H_res, saved, iters, eps, *, grads=None, d
     return dx, grads
 
 
+def dynamic_pre_fwd(x, rmsnorm_weight, phi, alpha, bias, iters, eps):
+    """mhc_dynamic_pre_fwd: first half of the split layer.  Returns (y_hat [B,C], saved) with saved
+    holding rms, rms_h, H_pre, H_post, M, proj (fp32)."""
+    tag = _dtype_tag(x)
+    _chk(x, "x", x.dtype)
+    B, n, C = x.shape
+    K = 2 * n + n * n
+    f32 = dict(dtype=torch.float32, device=x.device)
+    y_hat = _empty(B, C, dtype=x.dtype, device=x.device)
+    saved = {"rms": _empty(B, **f32), "rms_h": _empty(B, **f32), "H_pre": _empty(B, n, **f32),
+             "H_post": _empty(B, n, **f32), "M": _empty(B, n, n, **f32), "proj": _empty(B, K, **f32)}
+    ws = _workspace(workspace_bytes(L.OP_DYNAMIC_FWD, B, n, C, iters, tag), x.device)
+    st = L.lib().mhc_dynamic_pre_fwd(
+        _ptr(y_hat), _ptr(saved["rms"]), _ptr(saved["rms_h"]), _ptr(saved["H_pre"]),
+        _ptr(saved["H_post"]), _ptr(saved["M"]), _ptr(saved["proj"]), _ptr(x), _ptr(rmsnorm_weight),
+        _ptr(phi), _ptr(alpha), _ptr(bias), B, n, C, int(iters), float(eps), tag, _ptr(ws),
+        ws.numel(), _stream())
+    L.check(st, "mhc_dynamic_pre_fwd")
+    return y_hat, saved
+
+
+def post_fwd(x, f, H_post, M):
+    """mhc_post_fwd: y = M x + H_post f."""
+    tag = _dtype_tag(x)
+    B, n, C = x.shape
+    _chk(f, "f", x.dtype, (B, C))
+    y = _empty_like(x)
+    st = L.lib().mhc_post_fwd(_ptr(y), _ptr(x), _ptr(f), _ptr(H_post), _ptr(M), B, n, C, tag,
+                              _stream())
+    L.check(st, "mhc_post_fwd")
+    return y
+
+
+def post_bwd(dy, x, f, H_post, M):
+    """mhc_post_bwd: returns (dx_part, d_f, dH_post, dM)."""
+    tag = _dtype_tag(x)
+    B, n, C = x.shape
+    _chk(dy, "dy", x.dtype, x.shape)
+    f32 = dict(dtype=torch.float32, device=x.device)
+    dx_part, d_f = _empty_like(x), _empty_like(f)
+    dH_post, dM = _empty(B, n, **f32), _empty(B, n, n, **f32)
+    st = L.lib().mhc_post_bwd(_ptr(dx_part), _ptr(d_f), _ptr(dH_post), _ptr(dM), _ptr(dy), _ptr(x),
+                              _ptr(f), _ptr(H_post), _ptr(M), B, n, C, tag, _stream())
+    L.check(st, "mhc_post_bwd")
+    return dx_part, d_f, dH_post, dM
+
+
+def dynamic_pre_bwd(d_y_hat, dH_post, dM, x, rmsnorm_weight, phi, alpha, bias, saved, iters, eps):
+    """mhc_dynamic_pre_bwd: returns (dx, grads) with grads = d_rmsnorm_weight, d_phi, d_alpha, d_bias."""
+    tag = _dtype_tag(x)
+    B, n, C = x.shape
+    K = 2 * n + n * n
+    _chk(d_y_hat, "d_y_hat", x.dtype, (B, C))
+    f32 = dict(dtype=torch.float32, device=x.device)
+    grads = {"d_rmsnorm_weight": _empty(C, **f32), "d_phi": _empty(K, n * C, **f32),
+             "d_alpha": _empty(3, **f32), "d_bias": _empty(K, **f32)}
+    dx = _empty_like(x)
+    ws = _workspace(workspace_bytes(L.OP_DYNAMIC_PRE_BWD, B, n, C, iters, tag), x.device)
+    st = L.lib().mhc_dynamic_pre_bwd(
+        _ptr(dx), _ptr(grads["d_rmsnorm_weight"]), _ptr(grads["d_phi"]), _ptr(grads["d_alpha"]),
+        _ptr(grads["d_bias"]), _ptr(d_y_hat), _ptr(dH_post), _ptr(dM), _ptr(x), _ptr(rmsnorm_weight),
+        _ptr(phi), _ptr(alpha), _ptr(bias), _ptr(saved["rms"]), _ptr(saved["rms_h"]),
+        _ptr(saved["H_pre"]), _ptr(saved["H_post"]), _ptr(saved["proj"]), B, n, C, int(iters),
+        float(eps), tag, _ptr(ws), ws.numel(), _stream())
+    L.check(st, "mhc_dynamic_pre_bwd")
+    return dx, grads
+
+
 def _is_rect(inp):
     """A single 2-D matrix that the batched square kernels (n <= 32) do not cover."""
     return inp.dim() == 2 and (inp.shape[0] != inp.shape[1] or inp.shape[0] > 32)

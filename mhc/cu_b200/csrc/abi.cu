@@ -112,6 +112,25 @@ struct DynBwdWs {
     }
 };
 
+// first half of the split layer, backward: scalar coefficient kernels (n <= 8), fp32 dp, the
+// register dx kernel with its own number of d_weight rows
+struct PreBwdWs {
+    float *dH, *c2, *dpr, *qq, *partials, *dw_part;
+    void* den;
+    int nblk, ntb;
+    PreBwdWs(Carver& c, Dims d, int iters, int dtype) {
+        nblk = coeffs_thread_blocks(d);
+        ntb = dx_token_blocks(d);
+        dH = c.take<float>((size_t)d.B * d.K());
+        c2 = c.take<float>((size_t)d.B);
+        dpr = c.take<float>((size_t)d.B * d.K());
+        qq = c.take<float>((size_t)d.B);
+        partials = c.take<float>((size_t)nblk * (d.K() + 3));
+        dw_part = c.take<float>((size_t)ntb * d.C);
+        den = c.take_bytes((size_t)d.B * coeffs_thread_den_per_token(d, iters) * den_elem(dtype));
+    }
+};
+
 struct StaticFwdWs {
     float *hp, *hq, *M, *rms;
     StaticFwdWs(Carver& c, Dims d) {
@@ -253,6 +272,48 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
 }
 
 template <typename T>
+int pre_fwd_t(void* y_hat, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+              float* proj, const void* x, const void* w, const void* phi, const float* alpha,
+              const float* bias, Dims d, int iters, float eps, int dtype, void* workspace,
+              cudaStream_t s) {
+    Carver c(workspace);
+    DynFwdWs ws(c, d, dtype);
+    bool done = false;
+    if constexpr (std::is_same<T, bf16>::value) {
+        if (proj_mma_splits(d) != 0) {
+            MHC_TRY(launch_proj_mma(ws.praw, ws.sumsq, (const bf16*)x, (const bf16*)phi, d, s));
+            done = true;
+        }
+    }
+    if (!done) MHC_TRY(launch_proj<T>(ws.praw, ws.sumsq, (const T*)x, (const T*)phi, d, s));
+    MHC_TRY(launch_coeffs_dyn_fwd(H_pre, H_post, M, proj, rms_h, ws.praw, ws.sumsq, ws.nsplit, alpha,
+                                  bias, d, iters, eps, dtype == MHC_F32, s));
+    MHC_TRY(launch_pre_apply<T>((T*)y_hat, rms, (const T*)x, (const bf16*)w, H_pre, d, eps, s));
+    return MHC_OK;
+}
+
+template <typename T>
+int pre_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_bias, const void* dyh,
+              const float* dH_post, const float* dM, const void* x, const void* w, const void* phi,
+              const float* alpha, const float* bias, const float* rms, const float* rms_h,
+              const float* H_pre, const float* H_post, const float* proj, Dims d, int iters,
+              float eps, int dtype, void* workspace, cudaStream_t s) {
+    Carver c(workspace);
+    PreBwdWs ws(c, d, iters, dtype);
+    MHC_TRY(launch_pre_bwd_reduce<T>(ws.dH, ws.c2, (const T*)dyh, (const T*)x, (const bf16*)w, H_pre,
+                                     rms, dH_post, dM, d, s));
+    MHC_TRY(launch_coeffs_dyn_bwd_thread(ws.dpr, ws.qq, ws.partials, ws.dH, H_pre, H_post, proj, rms_h,
+                                         alpha, bias, ws.den, d, iters, eps, dtype == MHC_F32,
+                                         MmaBwdOut(), s));
+    MHC_TRY(launch_pre_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dyh, (const bf16*)w, H_pre,
+                                 rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d, s));
+    MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+    MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials, ws.nblk, d.n,
+                            s));
+    return MHC_OK;
+}
+
+template <typename T>
 int static_fwd_t(void* y, float* rms, float* hp, float* hq, float* M, const void* x, const void* w,
                  const float* H_pre, const float* H_post, const float* H_res, Dims d, int iters,
                  float eps, int dtype, cudaStream_t s) {
@@ -351,6 +412,11 @@ size_t mhc_workspace_bytes(int op, int64_t B, int n, int64_t C, int iters, int d
         case MHC_OP_DYNAMIC_BWD: { DynBwdWs w(c, d, iters, dtype); break; }
         case MHC_OP_STATIC_FWD: { StaticFwdWs w(c, d); break; }
         case MHC_OP_STATIC_BWD: { StaticBwdWs w(c, d, iters, dtype); break; }
+        case MHC_OP_DYNAMIC_PRE_BWD: {
+            if (d.n > 8) return (size_t)-1;
+            PreBwdWs w(c, d, iters, dtype);
+            break;
+        }
         case MHC_OP_SINKHORN_FWD: return 0;
         case MHC_OP_SINKHORN_BWD: return sinkhorn_bwd_ws(B, n, iters) + 256;
         default: return (size_t)-1;
@@ -510,6 +576,100 @@ int mhc_sinkhorn_rect_bwd(float* d_inp, const float* grad_out, const float* inp,
     MHC_TRY(launch_sinkhorn_rect_bwd(d_inp, grad_out, inp, workspace, M, N, iters, eps,
                                      reinterpret_cast<cudaStream_t>(stream)));
     return MHC_OK;
+}
+
+int mhc_dynamic_pre_fwd(void* y_hat, float* rms, float* rms_h, float* H_pre, float* H_post, float* M,
+                        float* proj, const void* x, const void* rmsnorm_weight, const void* phi,
+                        const float* alpha, const float* bias, int64_t B, int n, int64_t C,
+                        int iters, float eps, int dtype, void* workspace, size_t workspace_bytes,
+                        mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!rmsnorm_weight || !phi || !alpha || !bias) return MHC_ERR_NULL_POINTER;
+    if (B > 0 && (!y_hat || !rms || !rms_h || !H_pre || !H_post || !M || !proj || !x))
+        return MHC_ERR_NULL_POINTER;
+    if (B == 0) return MHC_OK;
+    const Dims d{B, n, C};
+    if (!split_ops_supported(d, dtype == MHC_F32 ? 4 : 2)) return MHC_ERR_UNSUPPORTED;
+    if (!aligned16(y_hat) || !aligned16(x) || !aligned16(phi) || !aligned16(rmsnorm_weight) ||
+        !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = mhc_workspace_bytes(MHC_OP_DYNAMIC_FWD, B, n, C, iters, dtype);
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return pre_fwd_t<float>(y_hat, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi,
+                                alpha, bias, d, iters, eps, dtype, workspace, s);
+    return pre_fwd_t<bf16>(y_hat, rms, rms_h, H_pre, H_post, M, proj, x, rmsnorm_weight, phi, alpha,
+                           bias, d, iters, eps, dtype, workspace, s);
+}
+
+int mhc_post_fwd(void* y, const void* x, const void* f, const float* H_post, const float* M,
+                 int64_t B, int n, int64_t C, int dtype, mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, 0, dtype)) return st;
+    if (B == 0) return MHC_OK;
+    if (!y || !x || !f || !H_post || !M) return MHC_ERR_NULL_POINTER;
+    const Dims d{B, n, C};
+    if (!split_ops_supported(d, dtype == MHC_F32 ? 4 : 2)) return MHC_ERR_UNSUPPORTED;
+    if (!aligned16(y) || !aligned16(x) || !aligned16(f)) return MHC_ERR_MISALIGNED;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        MHC_TRY(launch_post_fwd<float>((float*)y, (const float*)x, (const float*)f, H_post, M, d, s));
+    else
+        MHC_TRY(launch_post_fwd<bf16>((bf16*)y, (const bf16*)x, (const bf16*)f, H_post, M, d, s));
+    return MHC_OK;
+}
+
+int mhc_post_bwd(void* dx_part, void* d_f, float* dH_post, float* dM, const void* dy, const void* x,
+                 const void* f, const float* H_post, const float* M, int64_t B, int n, int64_t C,
+                 int dtype, mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, 0, dtype)) return st;
+    if (B == 0) return MHC_OK;
+    if (!dx_part || !d_f || !dH_post || !dM || !dy || !x || !f || !H_post || !M)
+        return MHC_ERR_NULL_POINTER;
+    const Dims d{B, n, C};
+    if (!split_ops_supported(d, dtype == MHC_F32 ? 4 : 2)) return MHC_ERR_UNSUPPORTED;
+    if (!aligned16(dx_part) || !aligned16(d_f) || !aligned16(dy) || !aligned16(x) || !aligned16(f))
+        return MHC_ERR_MISALIGNED;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        MHC_TRY(launch_post_bwd<float>((float*)dx_part, (float*)d_f, dH_post, dM, (const float*)dy,
+                                       (const float*)x, (const float*)f, H_post, M, d, s));
+    else
+        MHC_TRY(launch_post_bwd<bf16>((bf16*)dx_part, (bf16*)d_f, dH_post, dM, (const bf16*)dy,
+                                      (const bf16*)x, (const bf16*)f, H_post, M, d, s));
+    return MHC_OK;
+}
+
+int mhc_dynamic_pre_bwd(void* dx, float* d_rmsnorm_weight, float* d_phi, float* d_alpha,
+                        float* d_bias, const void* d_y_hat, const float* dH_post, const float* dM,
+                        const void* x, const void* rmsnorm_weight, const void* phi,
+                        const float* alpha, const float* bias, const float* rms,
+                        const float* rms_h, const float* H_pre, const float* H_post,
+                        const float* proj, int64_t B, int n, int64_t C, int iters, float eps,
+                        int dtype, void* workspace, size_t workspace_bytes, mhc_stream_t stream) {
+    if (int st = check_dims(B, n, C, iters, dtype)) return st;
+    if (!d_rmsnorm_weight || !d_phi || !d_alpha || !d_bias || !rmsnorm_weight || !phi || !alpha ||
+        !bias)
+        return MHC_ERR_NULL_POINTER;
+    if (B > 0 && (!dx || !d_y_hat || !dH_post || !dM || !x || !rms || !rms_h || !H_pre || !H_post ||
+                  !proj))
+        return MHC_ERR_NULL_POINTER;
+    const Dims d{B, n, C};
+    if (!split_ops_supported(d, dtype == MHC_F32 ? 4 : 2)) return MHC_ERR_UNSUPPORTED;
+    if (!aligned16(dx) || !aligned16(d_y_hat) || !aligned16(x) || !aligned16(phi) ||
+        !aligned16(d_phi) || !aligned16(rmsnorm_weight) || !aligned16(workspace))
+        return MHC_ERR_MISALIGNED;
+    const size_t need = mhc_workspace_bytes(MHC_OP_DYNAMIC_PRE_BWD, B, n, C, iters, dtype);
+    if (need == (size_t)-1) return MHC_ERR_UNSUPPORTED;
+    if (need > 0 && (!workspace || workspace_bytes < need)) return MHC_ERR_WORKSPACE;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == MHC_F32)
+        return pre_bwd_t<float>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, d_y_hat, dH_post, dM, x,
+                                rmsnorm_weight, phi, alpha, bias, rms, rms_h, H_pre, H_post, proj, d,
+                                iters, eps, dtype, workspace, s);
+    return pre_bwd_t<bf16>(dx, d_rmsnorm_weight, d_phi, d_alpha, d_bias, d_y_hat, dH_post, dM, x,
+                           rmsnorm_weight, phi, alpha, bias, rms, rms_h, H_pre, H_post, proj, d, iters,
+                           eps, dtype, workspace, s);
 }
 
 int mhc_p2p_alloc(void** ptr, size_t bytes, unsigned char handle[64]) {

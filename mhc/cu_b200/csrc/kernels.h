@@ -162,6 +162,29 @@ cudaError_t launch_sinkhorn_rect_fwd(float* out, const float* inp, int M, int N,
 cudaError_t launch_sinkhorn_rect_bwd(float* d_inp, const float* grad, const float* inp, void* ws,
                                      int M, int N, int iters, float eps, cudaStream_t s);
 
+// ---- split_ops.cu: the dynamic layer in two halves around a caller's sub-layer F (n <= 8) --------
+bool split_ops_supported(Dims d, size_t elem_bytes);
+template <typename T>
+cudaError_t launch_pre_apply(T* yhat, float* rho, const T* x, const bf16* w, const float* H_pre,
+                             Dims d, float eps, cudaStream_t s);
+template <typename T>
+cudaError_t launch_post_fwd(T* y, const T* x, const T* f, const float* H_post, const float* M,
+                            Dims d, cudaStream_t s);
+template <typename T>
+cudaError_t launch_post_bwd(T* dx_part, T* d_f, float* dH_post, float* dM, const T* g, const T* x,
+                            const T* f, const float* H_post, const float* M, Dims d,
+                            cudaStream_t s);
+template <typename T>
+cudaError_t launch_pre_bwd_reduce(float* dH, float* c2, const T* dyh, const T* x, const bf16* w,
+                                  const float* H_pre, const float* rho, const float* dH_post,
+                                  const float* dM, Dims d, cudaStream_t s);
+// stream_ops.cu: dx of the first half (no M^T g term; g is d_y_hat [B, C])
+template <typename T>
+cudaError_t launch_pre_bwd_dx(T* dx, float* dw_part, const T* x, const T* dyh, const bf16* w,
+                              const float* H_pre, const float* rho, const float* c2,
+                              const float* dpr, const float* qq, const T* phi, Dims d,
+                              cudaStream_t s);
+
 // ---- p2p_allreduce.cu: sum of the ranks' gradient buckets over NVLink peer memory ------------
 cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* const* flags, int rank,
                                  int world, int64_t count, unsigned seq, int* status,

@@ -235,7 +235,10 @@ bwd_reduce_kernel(float* __restrict__ dH, float* __restrict__ c2_out, const T* _
 constexpr int kDxTokens = 32;
 constexpr int kDxTY = 8;
 
-template <typename T, int V, int MAXN, bool DYNAMIC>
+// PRE: the first half of the split layer only.  g is d_y_hat [B, C], the gradient of the normalised
+// aggregate itself (it takes the place of sum_i H_post[i] g[i,:]), and the M^T g term, which belongs
+// to the second half, is left out.
+template <typename T, int V, int MAXN, bool DYNAMIC, bool PRE = false>
 __global__ void __launch_bounds__(256)
 bwd_dx_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restrict__ x,
               const T* __restrict__ g, const bf16* __restrict__ w, const float* __restrict__ H_pre,
@@ -266,34 +269,39 @@ bwd_dx_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restri
 #pragma unroll
         for (int i = 0; i < MAXN; ++i) {
             hp[i] = (i < n) ? H_pre[cb * n + i] : 0.f;
-            hq[i] = (i < n) ? H_post[cb * n + i] : 0.f;
+            hq[i] = (!PRE && i < n) ? H_post[cb * n + i] : 0.f;
 #pragma unroll
             for (int j = 0; j < MAXN; ++j)
-                m[i][j] = (i < n && j < n) ? M[cb * n * n + i * n + j] : 0.f;
+                m[i][j] = (!PRE && i < n && j < n) ? M[cb * n * n + i * n + j] : 0.f;
         }
         const float ri = 1.f / rms[b];
         const float c2b = c2[b];
         const T* xb = x + b * nC + c0;
-        const T* gb = g + b * nC + c0;
-        float xv[MAXN][V], gv[MAXN][V];
+        const T* gb = PRE ? g + b * C + c0 : g + b * nC + c0;
+        float xv[MAXN][V], gv[MAXN][V], gpre[V];
 #pragma unroll
         for (int i = 0; i < MAXN; ++i) {
             if (i < n) {
                 load_vec<V>(xb + i * C, xv[i]);
-                load_vec<V>(gb + i * C, gv[i]);
+                if constexpr (!PRE) load_vec<V>(gb + i * C, gv[i]);
             } else {
 #pragma unroll
-                for (int e = 0; e < V; ++e) { xv[i][e] = 0.f; gv[i][e] = 0.f; }
+                for (int e = 0; e < V; ++e) xv[i][e] = 0.f;
+            }
+            if (PRE || i >= n) {
+#pragma unroll
+                for (int e = 0; e < V; ++e) gv[i][e] = 0.f;
             }
         }
+        if constexpr (PRE) load_vec<V>(gb, gpre);
         float da[V];
 #pragma unroll
         for (int e = 0; e < V; ++e) {
-            float a = 0.f, dyh = 0.f;
+            float a = 0.f, dyh = PRE ? gpre[e] : 0.f;
 #pragma unroll
             for (int i = 0; i < MAXN; ++i) {
                 a = fmaf(hp[i], xv[i][e], a);
-                dyh = fmaf(hq[i], gv[i][e], dyh);
+                if constexpr (!PRE) dyh = fmaf(hq[i], gv[i][e], dyh);
             }
             da[e] = dyh * wv[e] * ri - a * c2b;
             dwacc[e] = fmaf(dyh * ri, a, dwacc[e]);
@@ -307,8 +315,10 @@ bwd_dx_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __restri
 #pragma unroll
                 for (int e = 0; e < V; ++e) {
                     float t = hp[j] * da[e];
+                    if constexpr (!PRE) {
 #pragma unroll
-                    for (int i = 0; i < MAXN; ++i) t = fmaf(m[i][j], gv[i][e], t);
+                        for (int i = 0; i < MAXN; ++i) t = fmaf(m[i][j], gv[i][e], t);
+                    }
                     if constexpr (DYNAMIC) t = fmaf(-qb, xv[j][e], t);
                     o[e] = t;
                 }
@@ -485,6 +495,35 @@ cudaError_t launch_bwd_dx(T* dx, float* dw_part, const T* x, const T* g, const b
 #undef MHC_DX
     return launched();
 }
+
+template <typename T>
+cudaError_t launch_pre_bwd_dx(T* dx, float* dw_part, const T* x, const T* dyh, const bf16* w,
+                              const float* H_pre, const float* rho, const float* c2,
+                              const float* dpr, const float* qq, const T* phi, Dims d,
+                              cudaStream_t s) {
+    if (d.B == 0) return cudaSuccess;
+    constexpr int VW = VecWidth<T>::value;
+    if (d.n > 8 || d.C % VW != 0) return cudaErrorNotSupported;
+    const int64_t nvec = d.C / VW;
+    const dim3 block(32, kDxTY);
+    const dim3 grid((unsigned)((nvec + 31) / 32), (unsigned)dx_token_blocks(d));
+    // H_post and M are not read in this mode (the pointers passed for them are H_pre's)
+    if (d.n <= 4)
+        bwd_dx_kernel<T, VW, 4, true, true><<<grid, block, 0, s>>>(dx, dw_part, x, dyh, w, H_pre, H_pre,
+                                                                   H_pre, 1, rho, c2, dpr, qq, phi,
+                                                                   d.B, d.n, d.C);
+    else
+        bwd_dx_kernel<T, VW, 8, true, true><<<grid, block, 0, s>>>(dx, dw_part, x, dyh, w, H_pre, H_pre,
+                                                                   H_pre, 1, rho, c2, dpr, qq, phi,
+                                                                   d.B, d.n, d.C);
+    return launched();
+}
+template cudaError_t launch_pre_bwd_dx<float>(float*, float*, const float*, const float*, const bf16*,
+                                              const float*, const float*, const float*, const float*,
+                                              const float*, const float*, Dims, cudaStream_t);
+template cudaError_t launch_pre_bwd_dx<bf16>(bf16*, float*, const bf16*, const bf16*, const bf16*,
+                                             const float*, const float*, const float*, const float*,
+                                             const float*, const bf16*, Dims, cudaStream_t);
 
 cudaError_t launch_finalize(float* d_w, const float* dw_part, int nparts, int64_t C, float* d_bias,
                             float* d_alpha, const float* partials, int nparts2, int n,

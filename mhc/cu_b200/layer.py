@@ -6,7 +6,8 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from .ops import mhc_layer_fused, mhc_layer_fused_dynamic, mhc_layer_fused_inference
+from .ops import (mhc_layer_fused, mhc_layer_fused_dynamic, mhc_layer_fused_inference, mhc_post,
+                  mhc_pre)
 
 
 class MHCLayer(nn.Module):
@@ -61,3 +62,31 @@ class MHCLayer(nn.Module):
                                              self.H_post, self.H_res, self.sinkhorn_iters, self.eps)
         return mhc_layer_fused(x_expanded, self.rmsnorm_weight, self.H_pre, self.H_post, self.H_res,
                                self.sinkhorn_iters, self.eps)
+
+
+class MHCBlock(nn.Module):
+    """A dynamic-H :class:`MHCLayer` wrapped around a sub-layer ``fn`` (attention, MLP, ...):
+
+        y_hat, H_post, M = pre(x)          aggregate the n streams, RMSNorm      [B, C]
+        f = fn(y_hat)                      the caller's module, any autograd     [B, C]
+        y = M x + H_post f                 distribute + mix                      [B, n, C]
+
+    The reference layer has no such hook (src/python/mhc/layer.py:61-101 computes distribute + mix
+    directly on the normalised aggregate); with ``fn = nn.Identity()`` this block computes exactly
+    what ``layer(x)`` computes.  The parameters are the wrapped layer's."""
+
+    def __init__(self, layer: MHCLayer, fn: nn.Module):
+        super().__init__()
+        if not layer.use_dynamic_h:
+            raise ValueError("MHCBlock needs a dynamic-H MHCLayer")
+        if layer.expansion_rate > 8:
+            raise ValueError("the split kernels cover expansion rates up to 8")
+        self.layer, self.fn = layer, fn
+
+    def forward(self, x_expanded: torch.Tensor) -> torch.Tensor:
+        L = self.layer
+        y_hat, H_post, M = mhc_pre(
+            x_expanded, L.rmsnorm_weight, L.phi_pre, L.phi_post, L.phi_res, L.alpha_pre,
+            L.alpha_post, L.alpha_res, L.b_pre, L.b_post, L.b_res, L.sinkhorn_iters, L.eps)
+        f = self.fn(y_hat)
+        return mhc_post(x_expanded, f, H_post, M)

@@ -211,3 +211,94 @@ def mhc_layer_fused_dynamic(x_expanded, rmsnorm_weight, phi_pre, phi_post, phi_r
         x_expanded.to(_compute_dtype(x_expanded)), rmsnorm_weight.bfloat16(), phi_pre.float(),
         phi_post.float(), phi_res.float(), alpha_pre, alpha_post, alpha_res, b_pre.float(),
         b_post.float(), b_res.float(), sinkhorn_iters, eps)
+
+
+# ---- the dynamic layer in two halves around a caller's sub-layer F -------------------------------
+class MHCPreFunction(Function):
+    """First half: apply(x, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post,
+    alpha_res, b_pre, b_post, b_res, sinkhorn_iters, eps) -> (y_hat [B, C], H_post [B, n],
+    M [B, n, n]).  y_hat feeds the sub-layer; H_post and M go to :class:`MHCPostFunction`, whose
+    backward hands their gradients back here."""
+
+    @staticmethod
+    def forward(ctx, x_expanded, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post,
+                alpha_res, b_pre, b_post, b_res, sinkhorn_iters, eps):
+        from . import capi
+        x = x_expanded.contiguous()
+        w = rmsnorm_weight.contiguous()
+        n = phi_pre.size(0)
+        phi = pack_phi(phi_pre, phi_post, phi_res, x.dtype)
+        dev = x.device
+        alpha = torch.stack([torch.as_tensor(a, dtype=torch.float32, device=dev).reshape(())
+                             for a in (alpha_pre, alpha_post, alpha_res)]).float()
+        bias = torch.cat([b_pre.reshape(-1), b_post.reshape(-1), b_res.reshape(-1)]).float()
+        y_hat, sv = capi.dynamic_pre_fwd(x, w, phi, alpha, bias, sinkhorn_iters, eps)
+        ctx.save_for_backward(x, w, phi, alpha, bias, sv["rms"], sv["rms_h"], sv["H_pre"],
+                              sv["H_post"], sv["proj"])
+        ctx.sinkhorn_iters, ctx.eps, ctx.n = sinkhorn_iters, eps, n
+        ctx.param_dtypes = (w.dtype, phi_pre.dtype, phi_post.dtype, phi_res.dtype,
+                            getattr(alpha_pre, "dtype", torch.float32),
+                            getattr(alpha_post, "dtype", torch.float32),
+                            getattr(alpha_res, "dtype", torch.float32),
+                            b_pre.dtype, b_post.dtype, b_res.dtype)
+        ctx.b_res_shape = tuple(b_res.shape)
+        ctx.phi_res_shape = tuple(phi_res.shape)
+        return y_hat, sv["H_post"], sv["M"]
+
+    @staticmethod
+    def backward(ctx, d_y_hat, dH_post, dM):
+        from . import capi
+        x, w, phi, alpha, bias, rms, rms_h, H_pre, H_post, proj = ctx.saved_tensors
+        B, n = x.shape[0], ctx.n
+        if d_y_hat is None:
+            d_y_hat = torch.zeros(B, x.shape[2], dtype=x.dtype, device=x.device)
+        if dH_post is None:
+            dH_post = torch.zeros(B, n, dtype=torch.float32, device=x.device)
+        if dM is None:
+            dM = torch.zeros(B, n, n, dtype=torch.float32, device=x.device)
+        saved = {"rms": rms, "rms_h": rms_h, "H_pre": H_pre, "H_post": H_post, "proj": proj}
+        dx, g = capi.dynamic_pre_bwd(d_y_hat.contiguous().to(x.dtype), dH_post.contiguous().float(),
+                                     dM.contiguous().float(), x, w, phi, alpha, bias, saved,
+                                     ctx.sinkhorn_iters, ctx.eps)
+        dt = ctx.param_dtypes
+        d_phi, d_alpha, d_bias = g["d_phi"], g["d_alpha"], g["d_bias"]
+        return (dx, g["d_rmsnorm_weight"].to(dt[0]),
+                d_phi[:n].to(dt[1]), d_phi[n:2 * n].to(dt[2]),
+                d_phi[2 * n:].reshape(ctx.phi_res_shape).to(dt[3]),
+                d_alpha[0].to(dt[4]), d_alpha[1].to(dt[5]), d_alpha[2].to(dt[6]),
+                d_bias[:n].to(dt[7]), d_bias[n:2 * n].to(dt[8]),
+                d_bias[2 * n:].reshape(ctx.b_res_shape).to(dt[9]), None, None)
+
+
+class MHCPostFunction(Function):
+    """Second half: apply(x, f, H_post, M) -> y = M x + H_post f, with f = F(y_hat) of shape [B, C]."""
+
+    @staticmethod
+    def forward(ctx, x_expanded, f, H_post, M):
+        from . import capi
+        x = x_expanded.contiguous()
+        f = f.contiguous().to(x.dtype)
+        H_post, M = H_post.contiguous(), M.contiguous()
+        ctx.save_for_backward(x, f, H_post, M)
+        return capi.post_fwd(x, f, H_post, M)
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        from . import capi
+        x, f, H_post, M = ctx.saved_tensors
+        dx_part, d_f, dH_post, dM = capi.post_bwd(grad_output.contiguous().to(x.dtype), x, f, H_post, M)
+        return dx_part, d_f, dH_post, dM
+
+
+def mhc_pre(x_expanded, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post, alpha_res,
+            b_pre, b_post, b_res, sinkhorn_iters=20, eps=1e-5):
+    """Aggregate + RMSNorm half of the dynamic layer: returns (y_hat, H_post, M)."""
+    return MHCPreFunction.apply(
+        x_expanded.to(_compute_dtype(x_expanded)), rmsnorm_weight.bfloat16(), phi_pre.float(),
+        phi_post.float(), phi_res.float(), alpha_pre, alpha_post, alpha_res, b_pre.float(),
+        b_post.float(), b_res.float(), sinkhorn_iters, eps)
+
+
+def mhc_post(x_expanded, f, H_post, M):
+    """Distribute + mix half: y[i] = sum_j M[i,j] x[j] + H_post[i] f."""
+    return MHCPostFunction.apply(x_expanded.to(_compute_dtype(x_expanded)), f, H_post, M)

@@ -14,6 +14,8 @@ from .naive_mhc import (  # noqa: F401
     sinkhorn_knopp,
     rmsnorm,
     mhc_dynamic,
+    mhc_dynamic_pre,
+    mhc_post,
     mhc_static,
     dynamic_fwd_bwd,
     static_fwd_bwd,

@@ -68,6 +68,27 @@ def mhc_dynamic(x, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_
     return _mix(x, H_pre, H_post, M, rmsnorm_weight, eps)
 
 
+def mhc_dynamic_pre(x, rmsnorm_weight, phi_pre, phi_post, phi_res, alpha_pre, alpha_post,
+                    alpha_res, b_pre, b_post, b_res, sinkhorn_iters=20, eps=1e-5):
+    """First half of the dynamic layer, for a sub-layer F applied between the halves: the
+    coefficients and the normalised aggregate ``y_hat = RMSNorm(sum_i H_pre[i] x[i,:]) * w``
+    ([B, C]).  Returns ``(y_hat, H_post, M)``.  The reference's layer is monolithic
+    (src/python/mhc/layer.py:61-101) with nothing between the two halves; with F = identity,
+    :func:`mhc_post` of this function's outputs is exactly :func:`mhc_dynamic`."""
+    H_pre, H_post, M = dynamic_coefficients(
+        x, phi_pre, phi_post, phi_res, alpha_pre, alpha_post, alpha_res,
+        b_pre, b_post, b_res, sinkhorn_iters, eps)
+    a = torch.einsum("bi,bic->bc", H_pre, x)
+    return rmsnorm(a, rmsnorm_weight.view(1, -1), eps), H_post, M
+
+
+def mhc_post(x, f, H_post, M):
+    """Second half: ``y[i,:] = sum_j M[i,j] x[j,:] + H_post[i] f`` with ``f = F(y_hat)`` ([B, C])
+    (the distribute + mix step of src/python/tests/test_layer.py:48-50 with F's output in place
+    of the normalised aggregate)."""
+    return torch.einsum("bij,bjc->bic", M, x) + H_post.unsqueeze(-1) * f.unsqueeze(1)
+
+
 def mhc_static(x, rmsnorm_weight, H_pre, H_post, H_res, sinkhorn_iters=20, eps=1e-5):
     """Static-H mHC layer: one sigmoid / 2*sigmoid / Sinkhorn(exp(.)) set of
     coefficients shared by all tokens (src/python/benchmarks/bench_layer.py:48-71)."""

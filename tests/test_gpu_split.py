@@ -1,0 +1,134 @@
+"""The dynamic layer in two halves (mhc_dynamic_pre_fwd/bwd, mhc_post_fwd/bwd) around a caller's
+sub-layer F, against the oracle's split functions and their autograd."""
+import pytest
+import torch
+
+import oracle
+from gpu_common import TOL
+from helpers import DYN_PARAMS, rel_err
+from mhc.cu_b200 import capi, synthetic
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(5, 4, 64, 0.5, 0.3), (33, 4, 256, 0.3, 0.2), (6, 8, 64, 0.4, 0.2), (4, 3, 24, 0.5, 0.3),
+          (64, 4, 2560, 0.2, 0.1)]
+
+
+def _sublayer(y_hat, Wf):
+    """A stand-in for F: a small dense map with a non-linearity, differentiable by autograd."""
+    return torch.tanh(y_hat @ Wf) * 0.5 + y_hat
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+@pytest.mark.parametrize("B,n,C,alpha,bs", SHAPES)
+def test_split_layer_matches_oracle(B, n, C, alpha, bs, dtype):
+    tol = TOL[dtype]
+    params = synthetic.dynamic_params(n, C, seed=1, alpha=alpha, bias_scale=bs, random_weight=True)
+    x, dy = synthetic.streams(B, n, C, seed=2)
+    gen = torch.Generator().manual_seed(3)
+    Wf = torch.randn(C, C, generator=gen) * (1.0 / C ** 0.5)
+    xq, dyq = x.to(dtype), dy.to(dtype)
+    w, phi, alpha_t, bias = synthetic.pack_dynamic(params, dtype, "cuda")
+
+    # ---- the CUDA path: pre -> F (torch, fp32 autograd on the device) -> post, and back -------------
+    xd, dyd = xq.cuda(), dyq.cuda()
+    y_hat, saved = capi.dynamic_pre_fwd(xd, w, phi, alpha_t, bias, 20, 1e-5)
+    yh = y_hat.float().requires_grad_(True)
+    f32 = _sublayer(yh, Wf.cuda())
+    f = f32.detach().to(dtype)
+    y = capi.post_fwd(xd, f, saved["H_post"], saved["M"])
+    dx_part, d_f, dH_post, dM = capi.post_bwd(dyd, xd, f, saved["H_post"], saved["M"])
+    (d_yh,) = torch.autograd.grad(f32, yh, grad_outputs=d_f.float())
+    dx_pre, grads = capi.dynamic_pre_bwd(d_yh.to(dtype), dH_post, dM, xd, w, phi, alpha_t, bias, saved,
+                                         20, 1e-5)
+    dx = dx_part.float() + dx_pre.float()
+
+    # ---- the oracle on the values the kernels consumed ------------------------------------------------
+    leaves = {"x": xq.double().requires_grad_(True)}
+    for k in DYN_PARAMS:
+        v = params[k]
+        if dtype == torch.bfloat16 and k.startswith("phi"):
+            v = v.bfloat16()
+        if k == "rmsnorm_weight":
+            v = v.bfloat16()
+        leaves[k] = v.double().clone().requires_grad_(True)
+    yh_ref, hq_ref, M_ref = oracle.mhc_dynamic_pre(leaves["x"], *[leaves[k] for k in DYN_PARAMS], 20, 1e-5)
+    y_ref = oracle.mhc_post(leaves["x"], _sublayer(yh_ref, Wf.double()), hq_ref, M_ref)
+    g = torch.autograd.grad(y_ref, list(leaves.values()), grad_outputs=dyq.double())
+    ref = dict(zip(["dx"] + ["d" + k for k in DYN_PARAMS], g))
+    n_ = n
+    got = {"y_hat": y_hat, "y": y, "dx": dx, "drmsnorm_weight": grads["d_rmsnorm_weight"],
+           "dphi_pre": grads["d_phi"][:n_], "dphi_post": grads["d_phi"][n_:2 * n_],
+           "dphi_res": grads["d_phi"][2 * n_:], "db_pre": grads["d_bias"][:n_],
+           "db_post": grads["d_bias"][n_:2 * n_], "db_res": grads["d_bias"][2 * n_:].view(n_, n_)}
+    want = dict(ref, y_hat=yh_ref.detach(), y=y_ref.detach())
+    # F runs in fp32 on bf16-rounded inputs here and in fp64 in the oracle: the bf16 tolerance covers it
+    errs = {k: rel_err(v, want[k]) for k, v in got.items()}
+    bad = {k: e for k, e in errs.items() if not e <= (tol if dtype == torch.bfloat16 else 2e-5)}
+    assert not bad, f"{bad}; all: {errs}"
+
+
+def test_split_with_identity_equals_the_layer():
+    """F = identity: pre + post reproduce mhc_dynamic_fwd bit for bit in y up to the rounding of y_hat."""
+    B, n, C = 16, 4, 256
+    params = synthetic.dynamic_params(n, C, seed=5, alpha=0.3, bias_scale=0.2)
+    x, _ = synthetic.streams(B, n, C, seed=6)
+    w, phi, alpha_t, bias = synthetic.pack_dynamic(params, torch.float32, "cuda")
+    xd = x.cuda()
+    y_full, _ = capi.dynamic_fwd(xd, w, phi, alpha_t, bias, 20, 1e-5)
+    y_hat, saved = capi.dynamic_pre_fwd(xd, w, phi, alpha_t, bias, 20, 1e-5)
+    y = capi.post_fwd(xd, y_hat, saved["H_post"], saved["M"])
+    assert rel_err(y, y_full.double().cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_mhc_block_autograd(dtype):
+    """mhc.MHCBlock(layer, fn): gradients of x, of the layer's and of fn's parameters through
+    autograd, against the same block built from the oracle's split functions."""
+    import mhc
+    torch.manual_seed(0)
+    B, n, C = 12, 4, 128
+    layer = mhc.MHCLayer(C, n).cuda()
+    with torch.no_grad():
+        for p_ in (layer.alpha_pre, layer.alpha_post, layer.alpha_res):
+            p_.fill_(0.4)
+        layer.b_pre.normal_(0, 0.2); layer.b_post.normal_(0, 0.2); layer.b_res.normal_(0, 0.2)
+    fn = torch.nn.Linear(C, C).cuda()
+    block = mhc.MHCBlock(layer, fn)
+    x = torch.randn(B, n, C, device="cuda").to(dtype).requires_grad_(True)
+    dy = torch.randn(B, n, C, device="cuda").to(dtype)
+    if dtype == torch.bfloat16:
+        block.fn = _Cast(fn)
+    y = block(x)
+    y.backward(dy)
+    # oracle
+    P = {k: v.detach().cpu() for k, v in layer.named_parameters()}
+    if dtype == torch.bfloat16:
+        for k in ("phi_pre", "phi_post", "phi_res"):
+            P[k] = P[k].bfloat16().float()
+    leaves = {k: P[k].double().requires_grad_(True) for k in DYN_PARAMS}
+    xr = x.detach().cpu().double().requires_grad_(True)
+    Wr = fn.weight.detach().cpu().double().requires_grad_(True)
+    br = fn.bias.detach().cpu().double().requires_grad_(True)
+    yh, hq, M = oracle.mhc_dynamic_pre(xr, *[leaves[k] for k in DYN_PARAMS], layer.sinkhorn_iters, layer.eps)
+    yr = oracle.mhc_post(xr, yh @ Wr.t() + br, hq, M)
+    yr.backward(dy.cpu().double())
+    tol = 2e-5 if dtype == torch.float32 else TOL[dtype]
+    errs = {"y": rel_err(y, yr.detach()), "dx": rel_err(x.grad, xr.grad),
+            "dW": rel_err(fn.weight.grad, Wr.grad), "dphi_res": rel_err(layer.phi_res.grad, leaves["phi_res"].grad),
+            "db_post": rel_err(layer.b_post.grad, leaves["b_post"].grad),
+            "dw": rel_err(layer.rmsnorm_weight.grad.float(), leaves["rmsnorm_weight"].grad)}
+    # the RMSNorm weight is a bf16 parameter, so autograd hands its gradient over in bf16
+    bad = {k: e for k, e in errs.items() if not e <= (max(tol, 8e-3) if k == "dw" else tol)}
+    assert not bad, f"{bad}; all: {errs}"
+
+
+class _Cast(torch.nn.Module):
+    """fp32 sub-layer behind bf16 streams."""
+
+    def __init__(self, inner):
+        super().__init__()
+        self.inner = inner
+
+    def forward(self, t):
+        return self.inner(t.float())
