@@ -92,7 +92,7 @@ struct DynBwdWs {
         int nblk_max = nblk > coeffs_lanes_blocks(d) ? nblk : coeffs_lanes_blocks(d);
         if (bwd_gram_supported(d) && bwd_gram_blocks(d) > nblk_max) nblk_max = bwd_gram_blocks(d);
         fused = mma && bwd_fused_supported(d);
-        ntb = fused ? bwd_fused_token_blocks(d) : (mma ? dx_mma_token_blocks(d) : dx_token_blocks(d));
+        ntb = fused ? bwd_fused_token_blocks(d) : dx_token_blocks(d);
         if (d.n > 8) ntb = (int)d.B;   // the wide dx pass leaves one d_weight row per token
         dphi_part = c.take<float>(fused && ntb > 1 ? (size_t)ntb * d.K() * d.nC() : 0);
         const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
@@ -117,7 +117,9 @@ struct DynBwdWs {
 struct PreBwdWs {
     float *dH, *c2, *dpr, *qq, *partials, *dw_part;
     void* den;
+    bf16* dprT;
     int nblk, ntb;
+    bool dphi_mma;
     PreBwdWs(Carver& c, Dims d, int iters, int dtype) {
         nblk = coeffs_thread_blocks(d);
         ntb = dx_token_blocks(d);
@@ -128,6 +130,10 @@ struct PreBwdWs {
         partials = c.take<float>((size_t)nblk * (d.K() + 3));
         dw_part = c.take<float>((size_t)ntb * d.C);
         den = c.take_bytes((size_t)d.B * coeffs_thread_den_per_token(d, iters) * den_elem(dtype));
+        // bf16, n = 4: d_phi on the tensor cores from a k-major bf16 copy of dpr
+        dphi_mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
+        const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
+        dprT = c.take<bf16>(dphi_mma ? Bp * bwd_mma_kp(d) : 0);
     }
 };
 
@@ -243,13 +249,9 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
             MHC_TRY(launch_dx_dphi_fused((bf16*)dx, d_phi, ws.dphi_part, ws.dw_part, (const bf16*)x,
                                          (const bf16*)dy, (const bf16*)w, ws.rec, ws.dprb, ws.dprT,
                                          (const bf16*)phi, d, s));
-        } else if (ws.mma) {
-            MHC_TRY(launch_dx_mma((bf16*)dx, ws.dw_part, (const bf16*)x, (const bf16*)dy,
-                                  (const bf16*)w, ws.rec, ws.dprb, (const bf16*)phi, d, s));
-            MHC_TRY(launch_dphi_mma(d_phi, (const bf16*)x, ws.dprT, d, s));
         }
     }
-    if (!ws.mma) {
+    if (!ws.fused) {
         if (d.n > 8)
             MHC_TRY(launch_bwd_dx_wide<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy,
                                           (const bf16*)w, H_pre, H_post, M, 1, rms, ws.c2, ws.dpr,
@@ -307,7 +309,15 @@ int pre_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_bias,
                                          MmaBwdOut(), s));
     MHC_TRY(launch_pre_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dyh, (const bf16*)w, H_pre,
                                  rms, ws.c2, ws.dpr, ws.qq, (const T*)phi, d, s));
-    MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+    bool dphi_done = false;
+    if constexpr (std::is_same<T, bf16>::value) {
+        if (ws.dphi_mma) {
+            MHC_TRY(launch_dpr_transpose(ws.dprT, ws.dpr, d, s));
+            MHC_TRY(launch_dphi_mma(d_phi, (const bf16*)x, ws.dprT, d, s));
+            dphi_done = true;
+        }
+    }
+    if (!dphi_done) MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
     MHC_TRY(launch_finalize(d_w, ws.dw_part, ws.ntb, d.C, d_bias, d_alpha, ws.partials, ws.nblk, d.n,
                             s));
     return MHC_OK;

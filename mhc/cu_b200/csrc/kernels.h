@@ -135,11 +135,9 @@ cudaError_t launch_proj_mma(float* praw_part, float* sumsq_part, const bf16* x, 
 bool bwd_mma_supported(Dims d);
 int bwd_mma_kp(Dims d);              // K rounded up to 8
 int bwd_mma_record_floats(Dims d);   // floats per token record
-int dx_mma_token_blocks(Dims d);     // rows of dw_part the dx pass writes
-cudaError_t launch_dx_mma(bf16* dx, float* dw_part, const bf16* x, const bf16* g, const bf16* w,
-                          const float* rec, const bf16* dprb, const bf16* phi, Dims d,
-                          cudaStream_t s);
 cudaError_t launch_dphi_mma(float* dphi, const bf16* x, const bf16* dprT, Dims d, cudaStream_t s);
+// bf16, k-major copy of the fp32 dpr [B][K] that launch_dphi_mma reads: dprT [KP][Bp], zero padded
+cudaError_t launch_dpr_transpose(bf16* dprT, const float* dpr, Dims d, cudaStream_t s);
 
 // ---- mix_fwd.cu: fused forward (coefficients + aggregate + RMSNorm + distribute/mix) -----------
 bool mix_fwd_supported(Dims d, size_t elem_bytes);
