@@ -81,11 +81,11 @@ struct DynFwdWs {
 };
 
 struct DynBwdWs {
-    float *dH, *c2, *dpr, *qq, *partials, *dw_part, *rec, *dphi_part;
+    float *dH, *c2, *dpr, *qq, *partials, *dw_part, *rec, *dphi_part, *t1;
     bf16 *dprb, *dprT;
     void* den;
     int nblk, ntb;
-    bool mma, fused;
+    bool mma, fused, wide_dphi_mma;
     DynBwdWs(Carver& c, Dims d, int iters, int dtype) {
         mma = (dtype == MHC_BF16) && bwd_mma_supported(d);
         nblk = d.n <= 8 ? coeffs_thread_blocks(d) : coeffs_dyn_bwd_blocks(d);
@@ -95,10 +95,13 @@ struct DynBwdWs {
         ntb = fused ? bwd_fused_token_blocks(d) : dx_token_blocks(d);
         if (d.n > 8) ntb = (int)d.B;   // the wide dx pass leaves one d_weight row per token
         dphi_part = c.take<float>(fused && ntb > 1 ? (size_t)ntb * d.K() * d.nC() : 0);
+        t1 = c.take<float>(d.n > 8 ? (size_t)d.B * d.nC() : 0);   // dpr x phi of the wide path
         const size_t Bp = (size_t)(d.B + 15) / 16 * 16;
         rec = c.take<float>(mma ? (size_t)d.B * bwd_mma_record_floats(d) : 0);
         dprb = c.take<bf16>(mma ? (size_t)d.B * bwd_mma_kp(d) : 0);
-        dprT = c.take<bf16>(mma ? Bp * bwd_mma_kp(d) : 0);
+        // bf16, n > 8: d_phi on the tensor-core kernel from a k-major bf16 copy of dpr
+        wide_dphi_mma = (dtype == MHC_BF16) && d.n > 8 && d.nC() % 8 == 0;
+        dprT = c.take<bf16>((mma || wide_dphi_mma) ? Bp * bwd_mma_kp(d) : 0);
         dH = c.take<float>((size_t)d.B * d.K());
         c2 = c.take<float>((size_t)d.B);
         dpr = c.take<float>((size_t)d.B * d.K());
@@ -255,12 +258,20 @@ int dynamic_bwd_t(void* dx, float* d_w, float* d_phi, float* d_alpha, float* d_b
         if (d.n > 8)
             MHC_TRY(launch_bwd_dx_wide<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy,
                                           (const bf16*)w, H_pre, H_post, M, 1, rms, ws.c2, ws.dpr,
-                                          ws.qq, (const T*)phi, d, s));
+                                          ws.qq, (const T*)phi, d, s, ws.t1));
         else
             MHC_TRY(launch_bwd_dx<T>((T*)dx, ws.dw_part, (const T*)x, (const T*)dy, (const bf16*)w,
                                      H_pre, H_post, M, 1, rms, ws.c2, ws.dpr, ws.qq, (const T*)phi,
                                      d, s));
-        MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
+        bool dphi_done = false;
+        if constexpr (std::is_same<T, bf16>::value) {
+            if (ws.wide_dphi_mma) {
+                MHC_TRY(launch_dpr_transpose(ws.dprT, ws.dpr, d, s));
+                MHC_TRY(launch_dphi_mma(d_phi, (const bf16*)x, ws.dprT, d, s));
+                dphi_done = true;
+            }
+        }
+        if (!dphi_done) MHC_TRY(launch_dphi<T>(d_phi, (const T*)x, ws.dpr, d, s));
     }
     DphiSum dsum;
     if (ws.fused && ws.ntb > 1) {

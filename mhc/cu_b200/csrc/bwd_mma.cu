@@ -24,28 +24,6 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void mma_1688(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(b0));
-}
-
-// 16-byte asynchronous copy global -> shared (Ampere-style cp.async, lands without occupying
-// registers); src_bytes = 0 writes zeros instead of reading.
-__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(
-                     (uint32_t)__cvta_generic_to_shared(dst_smem)),
-                 "l"(src), "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
 __device__ __forceinline__ uint32_t ldg_u32(const bf16* p) {
     return *reinterpret_cast<const uint32_t*>(p);
 }
@@ -158,6 +136,69 @@ dphi_mma_kernel(float* __restrict__ dphi, const bf16* __restrict__ x,
     }
 }
 
+// Many output rows (wide expansion rates: K = 1088 at n = 32) and few tokens: every warp owns whole
+// m16 row tiles of dphi for the block's 64 columns and walks ALL tokens itself, so nothing is
+// reduced across warps and each result is stored straight from the accumulators; the block's
+// slice of x (64 columns x B tokens) is re-read from L1 by the warps, from HBM once.
+__global__ void __launch_bounds__(kDphiWarps * 32)
+dphi_rows_mma_kernel(float* __restrict__ dphi, const bf16* __restrict__ x,
+                     const bf16* __restrict__ dprT, int64_t B, int64_t Bp, int K, int KP,
+                     int64_t nC) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int64_t col0 = (int64_t)blockIdx.x * kDphiCols;
+    const bool colin = (col0 + 8 * g) < nC;
+    const int64_t ngroups = (B + 15) / 16;
+    const int ntile = (KP + 15) / 16;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    const bf16* xcol = x + col0 + 8 * g;
+    for (int mt = warp; mt < ntile; mt += kDphiWarps) {
+        float acc[8][4];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[u][e] = 0.f;
+        const int r0 = 16 * mt + g, r1 = r0 + 8;
+        for (int64_t grp = 0; grp < ngroups; ++grp) {
+            const int64_t ta = grp * 16 + 2 * q;
+            uint4 xa = zero, xb = zero, xc = zero, xd = zero;
+            if (colin) {
+                if (ta < B) xa = *reinterpret_cast<const uint4*>(xcol + ta * nC);
+                if (ta + 1 < B) xb = *reinterpret_cast<const uint4*>(xcol + (ta + 1) * nC);
+                if (ta + 8 < B) xc = *reinterpret_cast<const uint4*>(xcol + (ta + 8) * nC);
+                if (ta + 9 < B) xd = *reinterpret_cast<const uint4*>(xcol + (ta + 9) * nC);
+            }
+            const uint32_t a0 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
+            const uint32_t a1 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
+            const uint32_t a2 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
+            const uint32_t a3 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
+            const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
+            const uint32_t wc[4] = {xc.x, xc.y, xc.z, xc.w}, wd[4] = {xd.x, xd.y, xd.z, xd.w};
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                const uint32_t b0e = prmt(wa[p], wb[p], 0x5410), b0o = prmt(wa[p], wb[p], 0x7632);
+                const uint32_t b1e = prmt(wc[p], wd[p], 0x5410), b1o = prmt(wc[p], wd[p], 0x7632);
+                mma_16816(acc[2 * p], a0, a1, a2, a3, b0e, b1e);
+                mma_16816(acc[2 * p + 1], a0, a1, a2, a3, b0o, b1o);
+            }
+        }
+        // same element map as dphi_mma_kernel: acc[u][0..1] -> row r0, columns 16q+u and 16q+8+u;
+        // acc[u][2..3] -> row r1
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int64_t ca = col0 + 16 * q + u, cb = ca + 8;
+            if (r0 < K) {
+                if (ca < nC) dphi[(int64_t)r0 * nC + ca] = acc[u][0];
+                if (cb < nC) dphi[(int64_t)r0 * nC + cb] = acc[u][1];
+            }
+            if (r1 < K) {
+                if (ca < nC) dphi[(int64_t)r1 * nC + ca] = acc[u][2];
+                if (cb < nC) dphi[(int64_t)r1 * nC + cb] = acc[u][3];
+            }
+        }
+    }
+}
+
 }  // namespace
 
 // ---- host side ---------------------------------------------------------------------------------
@@ -188,6 +229,11 @@ cudaError_t launch_dphi_mma(float* dphi, const bf16* x, const bf16* dprT, Dims d
     const int K = d.K(), KP = bwd_mma_kp(d);
     const int64_t Bp = (d.B + 15) / 16 * 16;
     const int64_t nC = d.nC();
+    if (KP > 8 * 32) {   // many rows: one block per 64 columns, row tiles dealt to the warps
+        dphi_rows_mma_kernel<<<(unsigned)((nC + kDphiCols - 1) / kDphiCols), kDphiWarps * 32, 0, s>>>(
+            dphi, x, dprT, d.B, Bp, K, KP, nC);
+        return launched();
+    }
     constexpr int MT16 = 2;
     const dim3 grid((unsigned)((nC + kDphiCols - 1) / kDphiCols),
                     (unsigned)((KP + MT16 * 16 - 1) / (MT16 * 16)));

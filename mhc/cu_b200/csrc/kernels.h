@@ -242,7 +242,8 @@ template <typename T>
 cudaError_t launch_bwd_dx_wide(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
                                const float* H_pre, const float* H_post, const float* M,
                                int coef_stride, const float* rms, const float* c2, const float* dpr,
-                               const float* qq, const T* phi, Dims d, cudaStream_t s);
+                               const float* qq, const T* phi, Dims d, cudaStream_t s,
+                               float* t1 = nullptr);   // t1: optional [B, nC] fp32 scratch
 
 // ---- rmsnorm.cu --------------------------------------------------------------------------------
 cudaError_t launch_rmsnorm_fwd(bf16* out, float* rms, const bf16* inp, const bf16* w, int64_t B,

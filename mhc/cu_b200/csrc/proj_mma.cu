@@ -161,8 +161,12 @@ int proj_mma_splits(Dims d) {
     const int64_t batch = (int64_t)kCH * kChunk;                  // 128 reduction elements
     const int64_t nbatch = (d.nC() + batch - 1) / batch;
     const int64_t groups = (d.B + kWarps * kTokens - 1) / (kWarps * kTokens);
-    // about two and a half blocks per SM; few splits when there are many tokens
-    int64_t want = (370 + groups - 1) / groups;
+    // about two and a half blocks per SM over token groups x output-tile groups x splits; few
+    // splits when the other two already fill the machine (every split is one more partial result
+    // of B x K floats that the consumer has to add up)
+    const int64_t tiles = (d.K() + 7) / 8;
+    const int64_t zgroups = tiles <= 4 ? 1 : (tiles + 4) / 5;
+    int64_t want = (370 + groups * zgroups - 1) / (groups * zgroups);
     if (want < 1) want = 1;
     if (want > nbatch) want = nbatch;
     int64_t nb = nbatch / want;

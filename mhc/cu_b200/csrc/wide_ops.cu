@@ -199,6 +199,61 @@ bwd_reduce_wide_kernel(float* __restrict__ dH, float* __restrict__ c2_out,
     }
 }
 
+// ---- t1[b, m] = sum_k dpr[b, k] phi[k, m]  (K = 2n + n^2 up to 1088, m over the n*C flat columns) ---
+// Block = 64 columns x up to 128 tokens, so phi is read ONCE per 128 tokens (one block per token
+// re-read all of phi for every token and was bound by that traffic).  dpr and phi arrive in
+// k-chunks of 32 through shared memory (dpr transposed: the 32 tokens of a thread are contiguous),
+// every thread keeps 32 token accumulators of its column.
+constexpr int kT1Cols = 64, kT1Tok = 128, kT1KC = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dp_phi_wide_kernel(float* __restrict__ t1, const float* __restrict__ dpr, const T* __restrict__ phi,
+                   int64_t B, int K, int64_t nC) {
+    __shared__ __align__(16) float dps[kT1KC][kT1Tok + 4];
+    __shared__ float phs[kT1KC][kT1Cols];   // the k-chunk of phi for the block's columns
+    const int tid = threadIdx.x, c = tid & 63, tg = tid >> 6;
+    const int64_t col = (int64_t)blockIdx.x * kT1Cols + c;
+    const int64_t tb = (int64_t)blockIdx.y * kT1Tok;
+    const bool colin = col < nC;
+    float acc[32];
+#pragma unroll
+    for (int t = 0; t < 32; ++t) acc[t] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += kT1KC) {
+        for (int i = tid; i < kT1Tok * kT1KC; i += 256) {
+            const int tok = i / kT1KC, kk = i % kT1KC;
+            const bool in = (tb + tok < B) && (k0 + kk < K);
+            dps[kk][tok] = in ? dpr[(tb + tok) * K + k0 + kk] : 0.f;
+        }
+        for (int i = tid; i < kT1KC * kT1Cols; i += 256) {
+            const int kk = i / kT1Cols, cc = i % kT1Cols;
+            const int64_t gc = (int64_t)blockIdx.x * kT1Cols + cc;
+            phs[kk][cc] = (k0 + kk < K && gc < nC) ? ldf<T>(phi + (int64_t)(k0 + kk) * nC + gc) : 0.f;
+        }
+        __syncthreads();
+        const int kmax = (K - k0 < kT1KC) ? K - k0 : kT1KC;
+        for (int kk = 0; kk < kmax; ++kk) {
+            const float pv = phs[kk][c];
+#pragma unroll
+            for (int t4 = 0; t4 < 8; ++t4) {
+                const float4 d4 = *reinterpret_cast<const float4*>(&dps[kk][tg * 32 + 4 * t4]);
+                acc[4 * t4 + 0] = fmaf(pv, d4.x, acc[4 * t4 + 0]);
+                acc[4 * t4 + 1] = fmaf(pv, d4.y, acc[4 * t4 + 1]);
+                acc[4 * t4 + 2] = fmaf(pv, d4.z, acc[4 * t4 + 2]);
+                acc[4 * t4 + 3] = fmaf(pv, d4.w, acc[4 * t4 + 3]);
+            }
+        }
+        __syncthreads();
+    }
+    if (colin) {
+#pragma unroll
+        for (int t = 0; t < 32; ++t) {
+            const int64_t b = tb + tg * 32 + t;
+            if (b < B) t1[b * nC + col] = acc[t];
+        }
+    }
+}
+
 // ---- backward pass B: dx and the per-token d_weight row, one block per token -------------------
 template <typename T, bool DYNAMIC>
 __global__ void __launch_bounds__(kWideThreads)
@@ -207,7 +262,8 @@ bwd_dx_wide_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __r
                    const float* __restrict__ H_pre, const float* __restrict__ H_post,
                    const float* __restrict__ M, int coef_stride, const float* __restrict__ rms,
                    const float* __restrict__ c2, const float* __restrict__ dpr,
-                   const float* __restrict__ qq, const T* __restrict__ phi, int n, int64_t C) {
+                   const float* __restrict__ qq, const T* __restrict__ phi,
+                   const float* __restrict__ t1, int n, int64_t C) {
     extern __shared__ float sm[];   // hp[n] hq[n] m[n*n] dp[K]
     const int K = 2 * n + n * n;
     float* hp = sm;
@@ -249,8 +305,12 @@ bwd_dx_wide_kernel(T* __restrict__ dx, float* __restrict__ dw_part, const T* __r
             for (int i = 0; i < kWMax; ++i)
                 if (i < n) t = fmaf(m[i * n + j], gc[i], t);
             if (DYNAMIC) {
-                const T* ph = phi + (int64_t)j * C + c;
-                for (int k = 0; k < K; ++k) t = fmaf(dp[k], ldf<T>(ph + (int64_t)k * nC), t);
+                if (t1 != nullptr) {   // the contraction against phi was done by dp_phi_wide_kernel
+                    t += t1[b * nC + (int64_t)j * C + c];
+                } else {
+                    const T* ph = phi + (int64_t)j * C + c;
+                    for (int k = 0; k < K; ++k) t = fmaf(dp[k], ldf<T>(ph + (int64_t)k * nC), t);
+                }
             }
             stf<T>(dx + b * nC + j * C + c, t);
         }
@@ -288,15 +348,24 @@ template <typename T>
 cudaError_t launch_bwd_dx_wide(T* dx, float* dw_part, const T* x, const T* g, const bf16* w,
                                const float* H_pre, const float* H_post, const float* M,
                                int coef_stride, const float* rms, const float* c2, const float* dpr,
-                               const float* qq, const T* phi, Dims d, cudaStream_t s) {
+                               const float* qq, const T* phi, Dims d, cudaStream_t s, float* t1) {
     if (d.B == 0) return cudaSuccess;
     const size_t smem = (size_t)(2 * d.n + d.n * d.n + d.K()) * sizeof(float);
-    if (phi != nullptr)
+    if (phi != nullptr) {
+        if (t1 != nullptr) {   // t1 [B, nC] fp32 scratch: dpr x phi as a blocked product first
+            const dim3 grid((unsigned)((d.nC() + kT1Cols - 1) / kT1Cols),
+                            (unsigned)((d.B + kT1Tok - 1) / kT1Tok));
+            dp_phi_wide_kernel<T><<<grid, 256, 0, s>>>(t1, dpr, phi, d.B, d.K(), d.nC());
+            const cudaError_t e = launched();
+            if (e != cudaSuccess) return e;
+        }
         bwd_dx_wide_kernel<T, true><<<(unsigned)d.B, kWideThreads, smem, s>>>(
-            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, d.n, d.C);
-    else
+            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, t1, d.n, d.C);
+    } else {
         bwd_dx_wide_kernel<T, false><<<(unsigned)d.B, kWideThreads, smem, s>>>(
-            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, d.n, d.C);
+            dx, dw_part, x, g, w, H_pre, H_post, M, coef_stride, rms, c2, dpr, qq, phi, nullptr, d.n,
+            d.C);
+    }
     return launched();
 }
 
@@ -310,7 +379,7 @@ cudaError_t launch_bwd_dx_wide(T* dx, float* dw_part, const T* x, const T* g, co
     template cudaError_t launch_bwd_dx_wide<T>(T*, float*, const T*, const T*, const bf16*,        \
                                                const float*, const float*, const float*, int,      \
                                                const float*, const float*, const float*,           \
-                                               const float*, const T*, Dims, cudaStream_t);
+                                               const float*, const T*, Dims, cudaStream_t, float*);
 MHC_INST(float)
 MHC_INST(bf16)
 #undef MHC_INST
