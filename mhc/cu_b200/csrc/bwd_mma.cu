@@ -159,28 +159,42 @@ dphi_rows_mma_kernel(float* __restrict__ dphi, const bf16* __restrict__ x,
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[u][e] = 0.f;
         const int r0 = 16 * mt + g, r1 = r0 + 8;
-        for (int64_t grp = 0; grp < ngroups; ++grp) {
+        struct Ops {
+            uint4 xa, xb, xc, xd;
+            uint32_t a0, a1, a2, a3;
+        };
+        auto fetch = [&](int64_t grp, Ops& o) {
             const int64_t ta = grp * 16 + 2 * q;
-            uint4 xa = zero, xb = zero, xc = zero, xd = zero;
+            o.xa = zero; o.xb = zero; o.xc = zero; o.xd = zero;
             if (colin) {
-                if (ta < B) xa = *reinterpret_cast<const uint4*>(xcol + ta * nC);
-                if (ta + 1 < B) xb = *reinterpret_cast<const uint4*>(xcol + (ta + 1) * nC);
-                if (ta + 8 < B) xc = *reinterpret_cast<const uint4*>(xcol + (ta + 8) * nC);
-                if (ta + 9 < B) xd = *reinterpret_cast<const uint4*>(xcol + (ta + 9) * nC);
+                if (ta < B) o.xa = *reinterpret_cast<const uint4*>(xcol + ta * nC);
+                if (ta + 1 < B) o.xb = *reinterpret_cast<const uint4*>(xcol + (ta + 1) * nC);
+                if (ta + 8 < B) o.xc = *reinterpret_cast<const uint4*>(xcol + (ta + 8) * nC);
+                if (ta + 9 < B) o.xd = *reinterpret_cast<const uint4*>(xcol + (ta + 9) * nC);
             }
-            const uint32_t a0 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
-            const uint32_t a1 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
-            const uint32_t a2 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
-            const uint32_t a3 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
-            const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wb[4] = {xb.x, xb.y, xb.z, xb.w};
-            const uint32_t wc[4] = {xc.x, xc.y, xc.z, xc.w}, wd[4] = {xd.x, xd.y, xd.z, xd.w};
+            o.a0 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta) : 0u;
+            o.a1 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta) : 0u;
+            o.a2 = (r0 < KP) ? ldg_u32(dprT + (int64_t)r0 * Bp + ta + 8) : 0u;
+            o.a3 = (r1 < KP) ? ldg_u32(dprT + (int64_t)r1 * Bp + ta + 8) : 0u;
+        };
+        Ops cur, nxt;
+        fetch(0, cur);
+        for (int64_t grp = 0; grp < ngroups; ++grp) {
+            // the next group's loads are in flight while this group's MMAs run
+            const bool more = grp + 1 < ngroups;
+            if (more) fetch(grp + 1, nxt);
+            const uint32_t wa[4] = {cur.xa.x, cur.xa.y, cur.xa.z, cur.xa.w};
+            const uint32_t wb[4] = {cur.xb.x, cur.xb.y, cur.xb.z, cur.xb.w};
+            const uint32_t wc[4] = {cur.xc.x, cur.xc.y, cur.xc.z, cur.xc.w};
+            const uint32_t wd[4] = {cur.xd.x, cur.xd.y, cur.xd.z, cur.xd.w};
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
                 const uint32_t b0e = prmt(wa[p], wb[p], 0x5410), b0o = prmt(wa[p], wb[p], 0x7632);
                 const uint32_t b1e = prmt(wc[p], wd[p], 0x5410), b1o = prmt(wc[p], wd[p], 0x7632);
-                mma_16816(acc[2 * p], a0, a1, a2, a3, b0e, b1e);
-                mma_16816(acc[2 * p + 1], a0, a1, a2, a3, b0o, b1o);
+                mma_16816(acc[2 * p], cur.a0, cur.a1, cur.a2, cur.a3, b0e, b1e);
+                mma_16816(acc[2 * p + 1], cur.a0, cur.a1, cur.a2, cur.a3, b0o, b1o);
             }
+            if (more) cur = nxt;
         }
         // same element map as dphi_mma_kernel: acc[u][0..1] -> row r0, columns 16q+u and 16q+8+u;
         // acc[u][2..3] -> row r1

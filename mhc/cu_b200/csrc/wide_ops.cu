@@ -200,11 +200,11 @@ bwd_reduce_wide_kernel(float* __restrict__ dH, float* __restrict__ c2_out,
 }
 
 // ---- t1[b, m] = sum_k dpr[b, k] phi[k, m]  (K = 2n + n^2 up to 1088, m over the n*C flat columns) ---
-// Block = 64 columns x up to 128 tokens, so phi is read ONCE per 128 tokens (one block per token
+// Block = 128 columns x up to 128 tokens, so phi is read ONCE per 128 tokens (one block per token
 // re-read all of phi for every token and was bound by that traffic).  dpr and phi arrive in
 // k-chunks of 32 through shared memory (dpr transposed: the 32 tokens of a thread are contiguous),
 // every thread keeps 32 token accumulators of its column.
-constexpr int kT1Cols = 64, kT1Tok = 128, kT1KC = 32;
+constexpr int kT1Cols = 128, kT1Tok = 128, kT1KC = 32;
 
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -212,13 +212,14 @@ dp_phi_wide_kernel(float* __restrict__ t1, const float* __restrict__ dpr, const 
                    int64_t B, int K, int64_t nC) {
     __shared__ __align__(16) float dps[kT1KC][kT1Tok + 4];
     __shared__ float phs[kT1KC][kT1Cols];   // the k-chunk of phi for the block's columns
+    // thread = columns c and c + 64 of the block, tokens [32 tg, 32 tg + 32): every value read from
+    // shared memory feeds two FMAs
     const int tid = threadIdx.x, c = tid & 63, tg = tid >> 6;
     const int64_t col = (int64_t)blockIdx.x * kT1Cols + c;
     const int64_t tb = (int64_t)blockIdx.y * kT1Tok;
-    const bool colin = col < nC;
-    float acc[32];
+    float acc0[32], acc1[32];
 #pragma unroll
-    for (int t = 0; t < 32; ++t) acc[t] = 0.f;
+    for (int t = 0; t < 32; ++t) { acc0[t] = 0.f; acc1[t] = 0.f; }
     for (int k0 = 0; k0 < K; k0 += kT1KC) {
         for (int i = tid; i < kT1Tok * kT1KC; i += 256) {
             const int tok = i / kT1KC, kk = i % kT1KC;
@@ -233,23 +234,28 @@ dp_phi_wide_kernel(float* __restrict__ t1, const float* __restrict__ dpr, const 
         __syncthreads();
         const int kmax = (K - k0 < kT1KC) ? K - k0 : kT1KC;
         for (int kk = 0; kk < kmax; ++kk) {
-            const float pv = phs[kk][c];
+            const float p0 = phs[kk][c], p1 = phs[kk][c + 64];
 #pragma unroll
             for (int t4 = 0; t4 < 8; ++t4) {
                 const float4 d4 = *reinterpret_cast<const float4*>(&dps[kk][tg * 32 + 4 * t4]);
-                acc[4 * t4 + 0] = fmaf(pv, d4.x, acc[4 * t4 + 0]);
-                acc[4 * t4 + 1] = fmaf(pv, d4.y, acc[4 * t4 + 1]);
-                acc[4 * t4 + 2] = fmaf(pv, d4.z, acc[4 * t4 + 2]);
-                acc[4 * t4 + 3] = fmaf(pv, d4.w, acc[4 * t4 + 3]);
+                acc0[4 * t4 + 0] = fmaf(p0, d4.x, acc0[4 * t4 + 0]);
+                acc0[4 * t4 + 1] = fmaf(p0, d4.y, acc0[4 * t4 + 1]);
+                acc0[4 * t4 + 2] = fmaf(p0, d4.z, acc0[4 * t4 + 2]);
+                acc0[4 * t4 + 3] = fmaf(p0, d4.w, acc0[4 * t4 + 3]);
+                acc1[4 * t4 + 0] = fmaf(p1, d4.x, acc1[4 * t4 + 0]);
+                acc1[4 * t4 + 1] = fmaf(p1, d4.y, acc1[4 * t4 + 1]);
+                acc1[4 * t4 + 2] = fmaf(p1, d4.z, acc1[4 * t4 + 2]);
+                acc1[4 * t4 + 3] = fmaf(p1, d4.w, acc1[4 * t4 + 3]);
             }
         }
         __syncthreads();
     }
-    if (colin) {
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-            const int64_t b = tb + tg * 32 + t;
-            if (b < B) t1[b * nC + col] = acc[t];
+    for (int t = 0; t < 32; ++t) {
+        const int64_t b = tb + tg * 32 + t;
+        if (b < B) {
+            if (col < nC) t1[b * nC + col] = acc0[t];
+            if (col + 64 < nC) t1[b * nC + col + 64] = acc1[t];
         }
     }
 }
