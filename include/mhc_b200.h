@@ -238,6 +238,15 @@ int mhc_grad_allreduce_p2p(float* out, const void* const* bufs, void* const* fla
                            int world, int64_t count, unsigned seq, int* status,
                            mhc_stream_t stream);
 
+/* The same with the step number kept on the device, for launches that are captured into a CUDA
+ * graph and replayed: `counter` (one 32-bit word of this rank's device memory, zero before the
+ * first call, touched by nothing else) holds the number of completed calls; the all-reduce uses
+ * counter + 1 as its step number and a one-thread kernel enqueued right behind it advances the
+ * counter.  All ranks have to make the same sequence of calls. */
+int mhc_grad_allreduce_p2p_counted(float* out, const void* const* bufs, void* const* flags, int rank,
+                                   int world, int64_t count, unsigned* counter, int* status,
+                                   mhc_stream_t stream);
+
 /* Same result as mhc_sinkhorn_bwd, for callers that cannot supply a workspace at all: a plug-in
  * inside a host that owns every byte of device memory and exposes no allocator, or a caller that
  * may not use cudaMalloc where it runs.  (No counterpart in AndreSlavescu/mHC.cu, whose bindings

@@ -43,6 +43,7 @@ SIGNATURES = {
     "mhc_p2p_close": (_i, [_p]),
     "mhc_p2p_free": (_i, [_p]),
     "mhc_grad_allreduce_p2p": (_i, [_p, _p, _p, _i, _i, _l, C.c_uint, _p, _p]),
+    "mhc_grad_allreduce_p2p_counted": (_i, [_p, _p, _p, _i, _i, _l, _p, _p, _p]),
     "mhc_sinkhorn_bwd_noalloc": (_i, [_p, _p, _p, _l, _i, _i, _f, _p]),
     "mhc_sinkhorn_bwd_noalloc_capacity": (_z, []),
     "mhc_rmsnorm_fwd": (_i, [_p, _p, _p, _p, _l, _l, _f, _p]),

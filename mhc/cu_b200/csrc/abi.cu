@@ -741,7 +741,23 @@ int mhc_grad_allreduce_p2p(float* out, const void* const* bufs, void* const* fla
     }
     if (!aligned16(out)) return MHC_ERR_MISALIGNED;
     if (count == 0) return MHC_OK;
-    MHC_TRY(launch_p2p_allreduce(out, bufs, flags, rank, world, count, seq, status,
+    MHC_TRY(launch_p2p_allreduce(out, bufs, flags, rank, world, count, seq, nullptr, status,
+                                 reinterpret_cast<cudaStream_t>(stream)));
+    return MHC_OK;
+}
+
+int mhc_grad_allreduce_p2p_counted(float* out, const void* const* bufs, void* const* flags, int rank,
+                                   int world, int64_t count, unsigned* counter, int* status,
+                                   mhc_stream_t stream) {
+    if (world < 1 || world > 16 || rank < 0 || rank >= world || count < 0) return MHC_ERR_BAD_SHAPE;
+    if (!out || !bufs || !flags || !counter) return MHC_ERR_NULL_POINTER;
+    for (int r = 0; r < world; ++r) {
+        if (!bufs[r] || !flags[r]) return MHC_ERR_NULL_POINTER;
+        if (!aligned16(bufs[r])) return MHC_ERR_MISALIGNED;
+    }
+    if (!aligned16(out)) return MHC_ERR_MISALIGNED;
+    if (count == 0) return MHC_OK;
+    MHC_TRY(launch_p2p_allreduce(out, bufs, flags, rank, world, count, 0u, counter, status,
                                  reinterpret_cast<cudaStream_t>(stream)));
     return MHC_OK;
 }

@@ -185,8 +185,8 @@ cudaError_t launch_pre_bwd_dx(T* dx, float* dw_part, const T* x, const T* dyh, c
 
 // ---- p2p_allreduce.cu: sum of the ranks' gradient buckets over NVLink peer memory ------------
 cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* const* flags, int rank,
-                                 int world, int64_t count, unsigned seq, int* status,
-                                 cudaStream_t s);
+                                 int world, int64_t count, unsigned seq, unsigned* counter,
+                                 int* status, cudaStream_t s);
 
 // ---- bwd_gram.cu: backward pass A from tensor-core Gram matrices (bf16, n = 4) --------------
 bool bwd_gram_supported(Dims d);

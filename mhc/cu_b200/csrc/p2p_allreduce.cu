@@ -55,9 +55,13 @@ struct P2PTable {
 
 __global__ void __launch_bounds__(kP2PThreads)
 p2p_allreduce_kernel(float* __restrict__ out, const P2PTable tab, int rank, int world, int64_t count,
-                     unsigned seq, int* __restrict__ status) {
+                     unsigned seq, const unsigned* __restrict__ counter, int* __restrict__ status) {
     __shared__ int ok_s;
     const int tid = threadIdx.x;
+    // step number from device memory (so that the launch can sit in a replayed CUDA graph): the
+    // counter holds the number of completed calls and is advanced by the one-thread kernel that
+    // follows this one in the stream
+    if (counter != nullptr) seq = *counter + 1u;
     if (blockIdx.x == 0 && tid < world) {
         __threadfence_system();
         st_release_sys(tab.flags[tid] + rank, seq);
@@ -107,11 +111,13 @@ p2p_allreduce_kernel(float* __restrict__ out, const P2PTable tab, int rank, int 
     }
 }
 
+__global__ void p2p_bump_kernel(unsigned* counter) { *counter += 1u; }
+
 }  // namespace
 
 cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* const* flags, int rank,
-                                 int world, int64_t count, unsigned seq, int* status,
-                                 cudaStream_t s) {
+                                 int world, int64_t count, unsigned seq, unsigned* counter,
+                                 int* status, cudaStream_t s) {
     if (world < 1 || world > kP2PMaxWorld || rank < 0 || rank >= world) return cudaErrorInvalidValue;
     P2PTable tab{};
     for (int r = 0; r < world; ++r) {
@@ -124,7 +130,12 @@ cudaError_t launch_p2p_allreduce(float* out, const void* const* bufs, void* cons
     if (blocks > 16) blocks = 16;
     if (blocks < 1) blocks = 1;
     p2p_allreduce_kernel<<<(unsigned)blocks, kP2PThreads, 0, s>>>(out, tab, rank, world, count, seq,
-                                                                status);
+                                                                counter, status);
+    if (counter != nullptr) {
+        const cudaError_t e = launched();
+        if (e != cudaSuccess) return e;
+        p2p_bump_kernel<<<1, 1, 0, s>>>(counter);
+    }
     return launched();
 }
 

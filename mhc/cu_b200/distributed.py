@@ -85,14 +85,17 @@ class PeerAllReduce:
     ``buckets[k]`` (k = 0, 1) are flat fp32 tensors of ``numel`` elements to write gradients into;
     consecutive steps must alternate between them.  ``all_reduce(k, out)`` leaves the sum over all
     ranks in ``out`` (a local tensor, default: an internal one returned by the call).  One rank per
-    GPU; the process group is only used to exchange the 64-byte handles at construction."""
+    GPU; the process group is used to exchange the 64-byte handles at construction and for the
+    barrier in ``close()``.  ``counted=True`` keeps the step number on the device so that the calls
+    can be captured into a CUDA graph."""
 
-    def __init__(self, numel: int, device, group=None):
+    def __init__(self, numel: int, device, group=None, counted: bool = False):
         import ctypes as C
 
         from . import _lib as L
         self._L, self._C = L, C
         lib = L.lib()
+        self._group, self._closed = group, False
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.numel, self.device = int(numel), torch.device(device)
         bucket_bytes = (self.numel * 4 + 255) // 256 * 256
@@ -138,14 +141,24 @@ class PeerAllReduce:
         self._out = torch.empty(self.numel, dtype=torch.float32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.seq = 0
+        # counted mode: the step number lives in device memory and is advanced by a kernel behind
+        # each all-reduce, so the calls may be captured into a CUDA graph and replayed
+        self.counter = (torch.zeros(1, dtype=torch.int32, device=self.device) if counted else None)
         dist.barrier(group=group)   # every rank has mapped every bucket before the first use
 
     def all_reduce(self, k: int, out=None, stream=None):
         out = self._out if out is None else out
         assert out.dtype == torch.float32 and out.numel() >= self.numel and out.is_contiguous()
-        self.seq += 1
         s = torch.cuda.current_stream(self.device).cuda_stream if stream is None else stream
         C = self._C
+        if self.counter is not None:
+            st = self._L.lib().mhc_grad_allreduce_p2p_counted(
+                C.c_void_p(out.data_ptr()), self._bufs[k], self._flags, self.rank, self.world,
+                self.numel, C.c_void_p(self.counter.data_ptr()), C.c_void_p(self.status.data_ptr()),
+                C.c_void_p(s))
+            self._L.check(st, "mhc_grad_allreduce_p2p_counted")
+            return out
+        self.seq += 1
         st = self._L.lib().mhc_grad_allreduce_p2p(
             C.c_void_p(out.data_ptr()), self._bufs[k], self._flags, self.rank, self.world,
             self.numel, C.c_uint(self.seq & 0xFFFFFFFF), C.c_void_p(self.status.data_ptr()),
@@ -161,8 +174,13 @@ class PeerAllReduce:
                                "not arrive within the wait limit)")
 
     def close(self):
+        """Collective: every rank calls it.  No rank frees its buckets before all ranks have
+        finished the kernels that read them."""
         lib = self._L.lib()
         torch.cuda.synchronize(self.device)
+        if not self._closed and dist.is_initialized():
+            dist.barrier(group=self._group)
+        self._closed = True
         for r, b in enumerate(self._peer_base):
             if r != self.rank:
                 lib.mhc_p2p_close(self._C.c_void_p(b))

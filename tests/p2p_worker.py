@@ -62,7 +62,41 @@ def main():
     torch.cuda.synchronize()
     t2 = torch.tensor([e0.elapsed_time(e1) * 1e3 / 200], device=dev)
     dist.all_reduce(t2, op=dist.ReduceOp.MAX)
+    # the counted variant (step number on the device) captured into a graph and replayed
+    par.close()
+    par = PeerAllReduce(numel, dev, counted=True)
+    src = [torch.zeros(numel, device=dev) for _ in range(2)]
+    res = [torch.zeros(numel, device=dev) for _ in range(2)]
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for k in range(2):   # one eager round first (also moves the counter off zero)
+            par.buckets[k].copy_(src[k])
+            par.all_reduce(k, out=res[k])
+        side.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            for k in range(2):
+                par.buckets[k].copy_(src[k])
+                par.all_reduce(k, out=res[k])
+        graph_ok = True
+        for rep in range(3):
+            want = []
+            for k in range(2):
+                src[k].copy_(torch.randn(numel, device=dev, generator=gen))
+                ref = src[k].clone()
+                dist.all_reduce(ref)
+                want.append(ref)
+            side.synchronize()
+            g.replay()
+            side.synchronize()
+            for k in range(2):
+                err = float((res[k] - want[k]).abs().max() / want[k].abs().max())
+                graph_ok = graph_ok and err < 1e-6
+    par.check_status()
+    graph_ok = graph_ok and int(par.counter.item()) == 2 + 3 * 2
+    ok = ok and graph_ok
     if rank == 0:
+        print(f"counted all-reduce in a replayed graph: {'ok' if graph_ok else 'BAD'}", flush=True)
         print(f"p2p all-reduce of {numel * 4 / 1e6:.2f} MB over {world} GPUs: parity {'ok' if ok else 'BAD'}, "
               f"identical bits on all ranks: {same}, {float(t):.1f} us per call "
               f"(NCCL all_reduce: {float(t2):.1f} us)", flush=True)
